@@ -1,0 +1,312 @@
+"""ctypes binding of the C ABI in include/b200tbe.h.
+
+The structures below mirror the header field by field. The helper functions take torch CUDA tensors
+only to read their data pointers and the current stream; every computation happens in
+libb200tbe.so. There is no fallback: if the library is missing, importing this module raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+
+import torch
+
+from . import _build
+
+MAX_DESTS = 16
+MAX_JAGGED_DIMS = 4
+
+FP32, FP16, INT8, INT4, INT2, BF16 = 0, 1, 2, 3, 4, 5
+POOL_SUM, POOL_MEAN, POOL_NONE = 0, 1, 2
+OPT_SGD, OPT_ROWWISE_ADAGRAD = 0, 1
+DEV_INDEX_OUT_OF_RANGE = 1
+
+_c_void_p = ctypes.c_void_p
+
+
+class ForwardParams(ctypes.Structure):
+    _fields_ = [
+        ("dev_weights", _c_void_p), ("weights_offsets", _c_void_p), ("D_offsets", _c_void_p),
+        ("rows_per_table", _c_void_p), ("indices", _c_void_p), ("offsets", _c_void_p),
+        ("per_sample_weights", _c_void_p), ("outputs", _c_void_p * MAX_DESTS),
+        ("output_stride", ctypes.c_int64), ("output_col_offset", ctypes.c_int64),
+        ("rows_per_dest", ctypes.c_int64), ("num_dests", ctypes.c_int32), ("T", ctypes.c_int32),
+        ("B", ctypes.c_int32), ("max_D", ctypes.c_int32), ("weights_dtype", ctypes.c_int32),
+        ("output_dtype", ctypes.c_int32), ("index_bytes", ctypes.c_int32),
+        ("pooling_mode", ctypes.c_int32), ("status", _c_void_p),
+    ]
+
+
+class NbitForwardParams(ctypes.Structure):
+    _fields_ = [
+        ("dev_weights", _c_void_p), ("weights_offsets", _c_void_p), ("weights_tys", _c_void_p),
+        ("D_offsets", _c_void_p), ("rows_per_table", _c_void_p), ("indices", _c_void_p),
+        ("offsets", _c_void_p), ("per_sample_weights", _c_void_p),
+        ("outputs", _c_void_p * MAX_DESTS), ("output_stride", ctypes.c_int64),
+        ("output_col_offset", ctypes.c_int64), ("rows_per_dest", ctypes.c_int64),
+        ("num_dests", ctypes.c_int32), ("T", ctypes.c_int32), ("B", ctypes.c_int32),
+        ("max_D", ctypes.c_int32), ("row_alignment", ctypes.c_int32),
+        ("output_dtype", ctypes.c_int32), ("index_bytes", ctypes.c_int32),
+        ("pooling_mode", ctypes.c_int32), ("status", _c_void_p),
+    ]
+
+
+class BackwardParams(ctypes.Structure):
+    _fields_ = [
+        ("dev_weights", _c_void_p), ("weights_offsets", _c_void_p), ("D_offsets", _c_void_p),
+        ("hash_size_cumsum", _c_void_p), ("indices", _c_void_p), ("offsets", _c_void_p),
+        ("per_sample_weights", _c_void_p), ("grad_output", _c_void_p),
+        ("grad_stride", ctypes.c_int64), ("grad_col_offset", ctypes.c_int64),
+        ("momentum1", _c_void_p), ("momentum1_offsets", _c_void_p),
+        ("num_indices", ctypes.c_int64), ("T", ctypes.c_int32), ("B", ctypes.c_int32),
+        ("max_D", ctypes.c_int32), ("total_hash_size_bits", ctypes.c_int32),
+        ("weights_dtype", ctypes.c_int32), ("grad_dtype", ctypes.c_int32),
+        ("index_bytes", ctypes.c_int32), ("pooling_mode", ctypes.c_int32),
+        ("optimizer", ctypes.c_int32), ("learning_rate", ctypes.c_float), ("eps", ctypes.c_float),
+        ("scratch", _c_void_p), ("scratch_bytes", ctypes.c_size_t), ("status", _c_void_p),
+    ]
+
+
+class JaggedShape(ctypes.Structure):
+    _fields_ = [
+        ("offsets", _c_void_p * MAX_JAGGED_DIMS), ("max_lengths", ctypes.c_int64 * MAX_JAGGED_DIMS),
+        ("num_jagged_dims", ctypes.c_int32), ("offset_bytes", ctypes.c_int32),
+        ("outer_size", ctypes.c_int64), ("inner_size", ctypes.c_int64),
+        ("total_rows", ctypes.c_int64), ("elem_bytes", ctypes.c_int32), ("dtype", ctypes.c_int32),
+    ]
+
+
+# Every symbol include/b200tbe.h declares; tests check that the library exports all of them.
+EXPORTS = (
+    "b200tbe_status_string", "b200tbe_abi_version", "b200tbe_forward", "b200tbe_nbit_forward",
+    "b200tbe_backward_scratch_bytes", "b200tbe_backward", "b200tbe_radix_sort_scratch_bytes",
+    "b200tbe_radix_sort_pairs", "b200tbe_jagged_to_padded_dense", "b200tbe_dense_to_jagged",
+    "b200tbe_jagged_dense_elementwise_add",
+)
+
+_lib = None
+
+
+def library_path() -> str:
+    return _build.CABI_LIB
+
+
+def lib() -> ctypes.CDLL:
+    """Loads libb200tbe.so (built in-tree beforehand). Raises if it is missing: there is no other
+    implementation to fall back to."""
+    global _lib
+    if _lib is None:
+        path = library_path()
+        if not os.path.exists(path):
+            raise RuntimeError(
+                "libb200tbe.so is not built (%s). Run `python -m torchlib_xpu_b200._build`; "
+                "the CUDA kernels are the only implementation of this package." % path)
+        _lib = ctypes.CDLL(path)
+        _lib.b200tbe_status_string.restype = ctypes.c_char_p
+        _lib.b200tbe_status_string.argtypes = [ctypes.c_int]
+        _lib.b200tbe_backward_scratch_bytes.restype = ctypes.c_size_t
+        _lib.b200tbe_backward_scratch_bytes.argtypes = [ctypes.c_int64, ctypes.c_int32]
+        _lib.b200tbe_radix_sort_scratch_bytes.restype = ctypes.c_size_t
+        _lib.b200tbe_radix_sort_scratch_bytes.argtypes = [ctypes.c_int64]
+        _lib.b200tbe_radix_sort_pairs.argtypes = [
+            _c_void_p, _c_void_p, _c_void_p, _c_void_p, ctypes.c_int64, ctypes.c_int32,
+            ctypes.c_int32, _c_void_p, ctypes.c_size_t, _c_void_p]
+        _lib.b200tbe_forward.argtypes = [ctypes.POINTER(ForwardParams), _c_void_p]
+        _lib.b200tbe_nbit_forward.argtypes = [ctypes.POINTER(NbitForwardParams), _c_void_p]
+        _lib.b200tbe_backward.argtypes = [ctypes.POINTER(BackwardParams), _c_void_p]
+        _lib.b200tbe_jagged_to_padded_dense.argtypes = [
+            ctypes.POINTER(JaggedShape), _c_void_p, _c_void_p, ctypes.c_uint64, _c_void_p]
+        _lib.b200tbe_dense_to_jagged.argtypes = [
+            ctypes.POINTER(JaggedShape), _c_void_p, _c_void_p, _c_void_p]
+        _lib.b200tbe_jagged_dense_elementwise_add.argtypes = [
+            ctypes.POINTER(JaggedShape), _c_void_p, _c_void_p, _c_void_p, _c_void_p]
+    return _lib
+
+
+class B200TbeError(RuntimeError):
+    pass
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        raise B200TbeError("%s: %s (%d)" % (what, lib().b200tbe_status_string(status).decode(), status))
+
+
+def _p(t):
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise B200TbeError("b200tbe entry points take CUDA tensors only")
+    if not t.is_contiguous():
+        raise B200TbeError("b200tbe entry points take contiguous tensors")
+    return t.data_ptr() or None
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+_TORCH_TO_CODE = {torch.float32: FP32, torch.float16: FP16, torch.bfloat16: BF16}
+_CODE_TO_TORCH = {FP32: torch.float32, FP16: torch.float16, BF16: torch.bfloat16}
+
+
+def _index_bytes(indices, offsets) -> int:
+    if indices.dtype != offsets.dtype or indices.dtype not in (torch.int64, torch.int32):
+        raise B200TbeError("indices and offsets must both be int64 or both int32")
+    return indices.element_size()
+
+
+def forward(dev_weights, weights_offsets, D_offsets, total_D, max_D, indices, offsets, B,
+            pooling_mode=POOL_SUM, per_sample_weights=None, output_dtype=torch.float32,
+            rows_per_table=None, status=None, outputs=None, output_stride=None,
+            output_col_offset=0, rows_per_dest=None):
+    """b200tbe_forward over torch tensors. Returns the [B, total_D] output (or `outputs` when the
+    caller supplies destination buffers)."""
+    T = weights_offsets.numel()
+    p = ForwardParams()
+    p.dev_weights, p.weights_offsets, p.D_offsets = _p(dev_weights), _p(weights_offsets), _p(D_offsets)
+    p.rows_per_table, p.indices, p.offsets = _p(rows_per_table), _p(indices), _p(offsets)
+    p.per_sample_weights = _p(per_sample_weights)
+    result = None
+    if outputs is None:
+        result = torch.empty((B, total_D), dtype=output_dtype, device=dev_weights.device)
+        outputs = [result]
+        output_stride, rows_per_dest = total_D, max(B, 1)
+    for i, o in enumerate(outputs):
+        p.outputs[i] = o if isinstance(o, int) else _p(o)
+    p.output_stride, p.output_col_offset, p.rows_per_dest = output_stride, output_col_offset, rows_per_dest
+    p.num_dests, p.T, p.B, p.max_D = len(outputs), T, B, max_D
+    p.weights_dtype = _TORCH_TO_CODE[dev_weights.dtype]
+    p.output_dtype = _TORCH_TO_CODE[output_dtype]
+    p.index_bytes = _index_bytes(indices, offsets)
+    p.pooling_mode = pooling_mode
+    p.status = _p(status)
+    check(lib().b200tbe_forward(ctypes.byref(p), _stream()), "b200tbe_forward")
+    return result if result is not None else outputs
+
+
+def nbit_forward(dev_weights, weights_offsets, weights_tys, D_offsets, total_D, max_D, indices,
+                 offsets, B, pooling_mode=POOL_SUM, per_sample_weights=None,
+                 output_dtype=torch.float16, row_alignment=16, rows_per_table=None, status=None):
+    T = weights_offsets.numel()
+    p = NbitForwardParams()
+    p.dev_weights, p.weights_offsets, p.weights_tys = _p(dev_weights), _p(weights_offsets), _p(weights_tys)
+    p.D_offsets, p.rows_per_table = _p(D_offsets), _p(rows_per_table)
+    p.indices, p.offsets, p.per_sample_weights = _p(indices), _p(offsets), _p(per_sample_weights)
+    out = torch.empty((B, total_D), dtype=output_dtype, device=dev_weights.device)
+    p.outputs[0] = _p(out)
+    p.output_stride, p.output_col_offset, p.rows_per_dest = total_D, 0, max(B, 1)
+    p.num_dests, p.T, p.B, p.max_D = 1, T, B, max_D
+    p.row_alignment = row_alignment
+    p.output_dtype = _TORCH_TO_CODE[output_dtype]
+    p.index_bytes = _index_bytes(indices, offsets)
+    p.pooling_mode = pooling_mode
+    p.status = _p(status)
+    check(lib().b200tbe_nbit_forward(ctypes.byref(p), _stream()), "b200tbe_nbit_forward")
+    return out
+
+
+def backward_scratch_bytes(num_indices: int, total_hash_size_bits: int) -> int:
+    return int(lib().b200tbe_backward_scratch_bytes(num_indices, total_hash_size_bits))
+
+
+def backward(dev_weights, weights_offsets, D_offsets, hash_size_cumsum, total_hash_size_bits, max_D,
+             indices, offsets, B, grad_output, optimizer, learning_rate, eps=0.0, momentum1=None,
+             momentum1_offsets=None, pooling_mode=POOL_SUM, per_sample_weights=None, scratch=None,
+             status=None, grad_col_offset=0):
+    """b200tbe_backward over torch tensors; dev_weights and momentum1 are updated in place."""
+    T = weights_offsets.numel()
+    n = indices.numel()
+    need = backward_scratch_bytes(n, total_hash_size_bits)
+    if scratch is None:
+        scratch = torch.empty(max(need, 256), dtype=torch.uint8, device=dev_weights.device)
+    p = BackwardParams()
+    p.dev_weights, p.weights_offsets, p.D_offsets = _p(dev_weights), _p(weights_offsets), _p(D_offsets)
+    p.hash_size_cumsum, p.indices, p.offsets = _p(hash_size_cumsum), _p(indices), _p(offsets)
+    p.per_sample_weights, p.grad_output = _p(per_sample_weights), _p(grad_output)
+    p.grad_stride, p.grad_col_offset = grad_output.stride(0), grad_col_offset
+    p.momentum1, p.momentum1_offsets = _p(momentum1), _p(momentum1_offsets)
+    p.num_indices, p.T, p.B, p.max_D = n, T, B, max_D
+    p.total_hash_size_bits = total_hash_size_bits
+    p.weights_dtype = _TORCH_TO_CODE[dev_weights.dtype]
+    p.grad_dtype = _TORCH_TO_CODE[grad_output.dtype]
+    p.index_bytes = _index_bytes(indices, offsets)
+    p.pooling_mode, p.optimizer = pooling_mode, optimizer
+    p.learning_rate, p.eps = learning_rate, eps
+    p.scratch, p.scratch_bytes = _p(scratch), scratch.numel()
+    p.status = _p(status)
+    check(lib().b200tbe_backward(ctypes.byref(p), _stream()), "b200tbe_backward")
+    return scratch
+
+
+def radix_sort_pairs(keys, vals, key_bits):
+    """Stable sort of (keys, vals) by the low key_bits bits. keys int32/int64, vals int32.
+    Returns new (keys, vals); the inputs are clobbered."""
+    n = keys.numel()
+    keys_out, vals_out = torch.empty_like(keys), torch.empty_like(vals)
+    need = int(lib().b200tbe_radix_sort_scratch_bytes(n))
+    scratch = torch.empty(max(need, 256), dtype=torch.uint8, device=keys.device)
+    check(lib().b200tbe_radix_sort_pairs(_p(keys), _p(vals), _p(keys_out), _p(vals_out), n,
+                                         keys.element_size(), key_bits, _p(scratch),
+                                         scratch.numel(), _stream()), "b200tbe_radix_sort_pairs")
+    return keys_out, vals_out
+
+
+def _jagged_shape(offsets_list, max_lengths, outer, inner, total_rows, elem_bytes, dtype_code):
+    if not 1 <= len(offsets_list) <= MAX_JAGGED_DIMS or len(offsets_list) != len(max_lengths):
+        raise B200TbeError("1..%d jagged dimensions with one max_length each" % MAX_JAGGED_DIMS)
+    s = JaggedShape()
+    ob = offsets_list[0].element_size()
+    for d, (o, m) in enumerate(zip(offsets_list, max_lengths)):
+        if o.dtype not in (torch.int64, torch.int32) or o.element_size() != ob:
+            raise B200TbeError("offsets must all be int64 or all int32")
+        s.offsets[d] = _p(o)
+        s.max_lengths[d] = int(m)
+    s.num_jagged_dims, s.offset_bytes = len(offsets_list), ob
+    s.outer_size, s.inner_size, s.total_rows = outer, inner, total_rows
+    s.elem_bytes, s.dtype = elem_bytes, dtype_code
+    return s
+
+
+def _pad_bits(value, dtype) -> int:
+    t = torch.tensor([value], dtype=dtype)
+    raw = t.view(torch.uint8).tolist()
+    return int.from_bytes(bytes(raw), "little")
+
+
+def jagged_to_padded_dense(values, offsets_list, max_lengths, padding_value=0.0):
+    outer = offsets_list[0].numel() - 1
+    inner = values.shape[1]
+    s = _jagged_shape(offsets_list, max_lengths, outer, inner, values.shape[0],
+                      values.element_size(), _TORCH_TO_CODE.get(values.dtype, -1))
+    dense = torch.empty((outer, *[int(m) for m in max_lengths], inner), dtype=values.dtype,
+                        device=values.device)
+    check(lib().b200tbe_jagged_to_padded_dense(ctypes.byref(s), _p(values), _p(dense),
+                                               _pad_bits(padding_value, values.dtype), _stream()),
+          "b200tbe_jagged_to_padded_dense")
+    return dense
+
+
+def dense_to_jagged(dense, offsets_list, total_rows):
+    n = len(offsets_list)
+    outer, inner = dense.shape[0], dense.shape[-1]
+    s = _jagged_shape(offsets_list, dense.shape[1:1 + n], outer, inner, total_rows,
+                      dense.element_size(), _TORCH_TO_CODE.get(dense.dtype, -1))
+    values = torch.empty((total_rows, inner), dtype=dense.dtype, device=dense.device)
+    check(lib().b200tbe_dense_to_jagged(ctypes.byref(s), _p(dense), _p(values), _stream()),
+          "b200tbe_dense_to_jagged")
+    return values
+
+
+def jagged_dense_elementwise_add(x_values, offsets_list, y):
+    n = len(offsets_list)
+    outer, inner = y.shape[0], y.shape[-1]
+    if x_values.dtype != y.dtype or x_values.dtype not in _TORCH_TO_CODE:
+        raise B200TbeError("jagged_dense_elementwise_add takes fp32, fp16 or bf16 of one dtype")
+    s = _jagged_shape(offsets_list, y.shape[1:1 + n], outer, inner, x_values.shape[0],
+                      y.element_size(), _TORCH_TO_CODE[y.dtype])
+    out = torch.empty_like(y)
+    check(lib().b200tbe_jagged_dense_elementwise_add(ctypes.byref(s), _p(x_values), _p(y), _p(out),
+                                                     _stream()),
+          "b200tbe_jagged_dense_elementwise_add")
+    return out
