@@ -62,6 +62,7 @@ typedef enum { B200TBE_OPT_SGD = 0, B200TBE_OPT_ROWWISE_ADAGRAD = 1 } b200tbe_op
 /* Bits a kernel may OR into the optional device status word (int32). */
 #define B200TBE_DEV_INDEX_OUT_OF_RANGE 1
 #define B200TBE_DEV_OFFSETS_NOT_MONOTONE 2
+#define B200TBE_DEV_UNSUPPORTED_SHAPE 4 /* a table's row is not whole 16-byte vectors */
 
 #define B200TBE_MAX_DESTS 16
 #define B200TBE_MAX_JAGGED_DIMS 4
@@ -191,13 +192,16 @@ typedef struct {
   int32_t* status;
 } b200tbe_backward_params;
 
-/* Scratch needed by b200tbe_backward for num_indices lookups (depends on nothing else). */
-B200TBE_API size_t b200tbe_backward_scratch_bytes(int64_t num_indices, int32_t total_hash_size_bits);
+/* Scratch needed by b200tbe_backward for num_indices lookups with keys of total_hash_size_bits
+ * bits and rows of at most max_D elements. */
+B200TBE_API size_t b200tbe_backward_scratch_bytes(int64_t num_indices, int32_t total_hash_size_bits,
+                                                  int32_t max_D);
 B200TBE_API int b200tbe_backward(const b200tbe_backward_params* p, b200tbe_stream_t stream);
 
 /* The sort of step (2) on its own: keys_in/vals_in are sorted by the low `key_bits` bits into
- * keys_out/vals_out (stable). key_bytes is 4 or 8; payloads are 4 bytes. All four arrays hold n
- * elements and must not alias; the inputs are overwritten (used as the ping-pong buffer). */
+ * keys_out/vals_out (stable; bits above key_bits are carried along but not compared). key_bytes is
+ * 4 or 8; payloads are 4 bytes. All four arrays hold n elements (n < 2^31) and must not alias; the
+ * inputs are overwritten (they are the ping-pong buffer). */
 B200TBE_API size_t b200tbe_radix_sort_scratch_bytes(int64_t n);
 B200TBE_API int b200tbe_radix_sort_pairs(void* keys_in, uint32_t* vals_in, void* keys_out,
                                          uint32_t* vals_out, int64_t n, int32_t key_bytes,

@@ -105,7 +105,7 @@ def lib() -> ctypes.CDLL:
         _lib.b200tbe_status_string.restype = ctypes.c_char_p
         _lib.b200tbe_status_string.argtypes = [ctypes.c_int]
         _lib.b200tbe_backward_scratch_bytes.restype = ctypes.c_size_t
-        _lib.b200tbe_backward_scratch_bytes.argtypes = [ctypes.c_int64, ctypes.c_int32]
+        _lib.b200tbe_backward_scratch_bytes.argtypes = [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32]
         _lib.b200tbe_radix_sort_scratch_bytes.restype = ctypes.c_size_t
         _lib.b200tbe_radix_sort_scratch_bytes.argtypes = [ctypes.c_int64]
         _lib.b200tbe_radix_sort_pairs.argtypes = [
@@ -206,8 +206,8 @@ def nbit_forward(dev_weights, weights_offsets, weights_tys, D_offsets, total_D, 
     return out
 
 
-def backward_scratch_bytes(num_indices: int, total_hash_size_bits: int) -> int:
-    return int(lib().b200tbe_backward_scratch_bytes(num_indices, total_hash_size_bits))
+def backward_scratch_bytes(num_indices: int, total_hash_size_bits: int, max_D: int) -> int:
+    return int(lib().b200tbe_backward_scratch_bytes(num_indices, total_hash_size_bits, max_D))
 
 
 def backward(dev_weights, weights_offsets, D_offsets, hash_size_cumsum, total_hash_size_bits, max_D,
@@ -217,7 +217,7 @@ def backward(dev_weights, weights_offsets, D_offsets, hash_size_cumsum, total_ha
     """b200tbe_backward over torch tensors; dev_weights and momentum1 are updated in place."""
     T = weights_offsets.numel()
     n = indices.numel()
-    need = backward_scratch_bytes(n, total_hash_size_bits)
+    need = backward_scratch_bytes(n, total_hash_size_bits, max_D)
     if scratch is None:
         scratch = torch.empty(max(need, 256), dtype=torch.uint8, device=dev_weights.device)
     p = BackwardParams()

@@ -1,0 +1,627 @@
+// TBE backward with the optimizer fused: exact (one update per distinct row) SGD / row-wise Adagrad.
+//
+//   linearize   one warp per bag: key = hash_size_cumsum[t] + index, payload = bag id (or the
+//               lookup position when per-sample weights are in use)
+//   sort        radix_sort.cu over total_hash_size_bits bits; sorted order is (table, row), so
+//               while one table's rows are being reduced only that table's slice of the gradient
+//               matrix (B x D_t) is live and stays in L2
+//   segment     head flags + compaction give the start of every run of equal keys
+//   reduce      persistent grid, one warp per run: the gradient slices of the run's bags are summed
+//               in sorted order with 16-byte loads (sub-warp groups when a slice is narrower than
+//               512 bytes), then the row and its optimizer state are read, updated and written once.
+//               Runs longer than kLongRun are cut into chunks of kLongRun lookups; a second kernel
+//               reduces each chunk to a partial row in scratch and a third adds a run's partials in
+//               chunk order and applies the update. Summation order is fixed by the data alone.
+#include "radix_sort.cuh"
+#include "scan.cuh"
+#include "tbe_pool.cuh"
+
+namespace b200tbe {
+namespace {
+
+constexpr int kBwdWarps = 8;
+constexpr int kBwdThreads = kBwdWarps * 32;
+constexpr int kLongRun = 512;           // lookups per chunk of a long run
+constexpr int kSegThreads = 1024;
+constexpr int kSegItems = 4;
+constexpr int kSegTile = kSegThreads * kSegItems;
+constexpr uint32_t kInvalidPayload = 0xffffffffu;
+
+struct BwdDev {
+  char* dev_weights;
+  const int64_t* weights_offsets;
+  const int32_t* D_offsets;
+  const int64_t* hash_size_cumsum;
+  const void* indices;
+  const void* offsets;
+  const float* per_sample_weights;
+  const char* grad_output;
+  int64_t grad_stride;
+  int64_t grad_col_offset;
+  float* momentum1;
+  const int64_t* momentum1_offsets;
+  int64_t num_indices;
+  int32_t T;
+  int32_t B;
+  int32_t pooling_mode;
+  int32_t optimizer;
+  int32_t index_bytes;
+  float learning_rate;
+  float eps;
+  int32_t* status;
+  // scratch
+  const void* sorted_keys;
+  const uint32_t* sorted_vals;
+  uint32_t* bag_of_pos;      // only with per-sample weights
+  uint32_t* run_start;       // [num_runs + 1]
+  uint32_t* counters;        // [0] runs, [1] long runs, [2] chunks
+  uint32_t* long_run;        // [max_long] run id of each long run
+  uint32_t* long_chunk0;     // [max_long] first chunk of each long run
+  uint32_t* chunk_run;       // [max_chunks] slot (index into long_run) of each chunk
+  float* partials;           // [max_chunks][max_D]
+  int32_t max_D;
+};
+
+// ---- linearize -----------------------------------------------------------------------------
+template <typename KeyT, typename IndexT, bool kWeighted>
+__global__ void __launch_bounds__(kBwdThreads)
+    linearize_kernel(BwdDev p, KeyT* __restrict__ keys, uint32_t* __restrict__ vals) {
+  const int lane = threadIdx.x & 31;
+  const int64_t bag = static_cast<int64_t>(blockIdx.x) * kBwdWarps + (threadIdx.x >> 5);
+  if (bag >= static_cast<int64_t>(p.T) * p.B) return;
+  const int t = static_cast<int>(bag / p.B);
+  const int64_t h0 = __ldg(p.hash_size_cumsum + t);
+  const int64_t rows = __ldg(p.hash_size_cumsum + t + 1) - h0;
+  const int64_t start = load_index<IndexT>(p.offsets, bag);
+  const int64_t end = load_index<IndexT>(p.offsets, bag + 1);
+  for (int64_t j = start + lane; j < end; j += 32) {
+    int64_t idx = load_index<IndexT>(p.indices, j);
+    uint32_t payload = kWeighted ? static_cast<uint32_t>(j) : static_cast<uint32_t>(bag);
+    if (idx < 0 || idx >= rows) {
+      if (p.status != nullptr) atomicOr(p.status, B200TBE_DEV_INDEX_OUT_OF_RANGE);
+      idx = 0;
+      payload = kInvalidPayload;
+    }
+    keys[j] = static_cast<KeyT>(h0 + idx);
+    vals[j] = payload;
+    if (kWeighted) p.bag_of_pos[j] = static_cast<uint32_t>(bag);
+  }
+}
+
+// ---- run-length segmentation --------------------------------------------------------------
+template <typename KeyT>
+__device__ __forceinline__ bool is_head(const KeyT* keys, int64_t i) {
+  return i == 0 || keys[i] != keys[i - 1];
+}
+
+template <typename KeyT>
+__global__ void __launch_bounds__(kSegThreads)
+    count_heads_kernel(const KeyT* __restrict__ keys, int64_t n, uint32_t* __restrict__ tile_heads) {
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * kSegTile + threadIdx.x * kSegItems;
+  uint32_t c = 0;
+#pragma unroll
+  for (int i = 0; i < kSegItems; ++i)
+    if (base + i < n && is_head(keys, base + i)) ++c;
+  uint32_t total;
+  block_exclusive_scan(c, &total);
+  if (threadIdx.x == 0) tile_heads[blockIdx.x] = total;
+}
+
+// tile_heads holds the exclusive scan of the per-tile head counts; counters[0] the total.
+template <typename KeyT>
+__global__ void __launch_bounds__(kSegThreads)
+    write_run_starts_kernel(const KeyT* __restrict__ keys, int64_t n,
+                            const uint32_t* __restrict__ tile_heads,
+                            const uint32_t* __restrict__ counters, uint32_t* __restrict__ run_start) {
+  const int64_t base = static_cast<int64_t>(blockIdx.x) * kSegTile + threadIdx.x * kSegItems;
+  bool head[kSegItems];
+  uint32_t c = 0;
+#pragma unroll
+  for (int i = 0; i < kSegItems; ++i) {
+    head[i] = base + i < n && is_head(keys, base + i);
+    c += head[i] ? 1u : 0u;
+  }
+  uint32_t total;
+  uint32_t at = block_exclusive_scan(c, &total) + tile_heads[blockIdx.x];
+#pragma unroll
+  for (int i = 0; i < kSegItems; ++i)
+    if (head[i]) run_start[at++] = static_cast<uint32_t>(base + i);
+  if (blockIdx.x == 0 && threadIdx.x == 0) run_start[counters[0]] = static_cast<uint32_t>(n);
+}
+
+// ---- gradient accumulation over a range of sorted lookups ------------------------------------
+// Sums, for sorted positions [s, e), the gradient slice of each lookup's bag (scaled by 1/L for
+// MEAN pooling and by the per-sample weight) into acc. Lane (g, v): group g takes every
+// rows_per_step-th lookup, v indexes the 16-byte vector inside the slice.
+__device__ __forceinline__ int64_t bag_length(const BwdDev& p, int64_t bag) {
+  if (p.index_bytes == 8)
+    return load_index<int64_t>(p.offsets, bag + 1) - load_index<int64_t>(p.offsets, bag);
+  return load_index<int32_t>(p.offsets, bag + 1) - load_index<int32_t>(p.offsets, bag);
+}
+
+template <typename GT, int kVPL>
+__device__ __forceinline__ void accumulate_range(const BwdDev& p, float (&acc)[kVPL][RowVec<GT>::kElems],
+                                                 int64_t s, int64_t e, int t, int gs, int slice_vecs,
+                                                 const char* grad_col, int lane) {
+  constexpr int kUnroll = kVPL == 1 ? 4 : (kVPL == 2 ? 2 : 1);
+  const int rows_per_step = 32 / gs;
+  const int g = lane / gs;
+  const int v = lane - g * gs;
+  const bool mean = p.pooling_mode == B200TBE_POOL_MEAN;
+  const bool weighted = p.per_sample_weights != nullptr;
+  const int64_t bag0 = static_cast<int64_t>(t) * p.B;
+  for (int64_t c = s; c < e; c += 32) {
+    const int n = e - c < 32 ? static_cast<int>(e - c) : 32;
+    int64_t my_row = -1;  // batch row of this lane's lookup
+    float my_w = 1.f;
+    if (lane < n) {
+      uint32_t payload = __ldg(p.sorted_vals + c + lane);
+      if (payload != kInvalidPayload) {
+        int64_t bag;
+        if (weighted) {
+          my_w = __ldg(p.per_sample_weights + payload);
+          bag = __ldg(p.bag_of_pos + payload);
+        } else {
+          bag = payload;
+        }
+        my_row = bag - bag0;
+        if (mean) my_w /= static_cast<float>(bag_length(p, bag));
+      }
+    }
+    for (int j = 0; j < n; j += rows_per_step * kUnroll) {
+      uint4 buf[kUnroll][kVPL];
+      float w[kUnroll];
+      bool ok[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int rr = j + u * rows_per_step + g;
+        const int64_t row = __shfl_sync(kFullMask, my_row, rr & 31);
+        w[u] = __shfl_sync(kFullMask, my_w, rr & 31);
+        ok[u] = rr < n && row >= 0;
+        if (ok[u]) {
+          const char* src = grad_col + row * p.grad_stride * static_cast<int64_t>(sizeof(GT));
+#pragma unroll
+          for (int k = 0; k < kVPL; ++k) {
+            const int vv = k * 32 + v;
+            if (vv < slice_vecs) buf[u][k] = ldg_stream16(src + (static_cast<int64_t>(vv) << 4));
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        if (ok[u]) {
+#pragma unroll
+          for (int k = 0; k < kVPL; ++k) {
+            if (k * 32 + v < slice_vecs) {
+              RowVec<GT>::fma(acc[k], buf[u][k], w[u]);  // w is exactly 1 when unweighted
+            }
+          }
+        }
+      }
+    }
+  }
+}
+
+template <typename WT>
+__device__ __forceinline__ void update_elems4(WT* w, const float* g, float mult);
+template <>
+__device__ __forceinline__ void update_elems4<float>(float* w, const float* g, float mult) {
+  float4 x = *reinterpret_cast<float4*>(w);
+  x.x = fmaf(-mult, g[0], x.x);
+  x.y = fmaf(-mult, g[1], x.y);
+  x.z = fmaf(-mult, g[2], x.z);
+  x.w = fmaf(-mult, g[3], x.w);
+  *reinterpret_cast<float4*>(w) = x;
+}
+template <>
+__device__ __forceinline__ void update_elems4<__half>(__half* w, const float* g, float mult) {
+  uint2 raw = *reinterpret_cast<uint2*>(w);
+  float2 a = half2_bits_to_float2(raw.x), b = half2_bits_to_float2(raw.y);
+  a.x = fmaf(-mult, g[0], a.x);
+  a.y = fmaf(-mult, g[1], a.y);
+  b.x = fmaf(-mult, g[2], b.x);
+  b.y = fmaf(-mult, g[3], b.y);
+  raw.x = float2_to_half2_bits(a.x, a.y);  // round to nearest even
+  raw.y = float2_to_half2_bits(b.x, b.y);
+  *reinterpret_cast<uint2*>(w) = raw;
+}
+
+// Applies the optimizer to one row given its summed gradient, held by the lanes of group 0
+// (lane v < slice_vecs holds elements [v*kE, (v+1)*kE) of vector k).
+template <typename WT, int kE, int kVPL>
+__device__ __forceinline__ void apply_update(const BwdDev& p, float (&acc)[kVPL][kE], int t,
+                                             int64_t row, int D, int gs, int slice_vecs, int lane) {
+  const int g = lane / gs;
+  const int v = lane - g * gs;
+  float mult = p.learning_rate;
+  if (p.optimizer == B200TBE_OPT_ROWWISE_ADAGRAD) {
+    float sq = 0.f;
+    if (g == 0) {
+#pragma unroll
+      for (int k = 0; k < kVPL; ++k)
+        if (k * 32 + v < slice_vecs)
+#pragma unroll
+          for (int e = 0; e < kE; ++e) sq = fmaf(acc[k][e], acc[k][e], sq);
+    }
+    sq = warp_sum(sq);
+    float* m = p.momentum1 + __ldg(p.momentum1_offsets + t) + row;
+    float m_new = 0.f;
+    if (lane == 0) {
+      m_new = *m + sq / static_cast<float>(D);
+      *m = m_new;
+    }
+    m_new = __shfl_sync(kFullMask, m_new, 0);
+    mult = p.learning_rate / (sqrtf(m_new) + p.eps);
+  }
+  if (g == 0) {
+    WT* w = reinterpret_cast<WT*>(p.dev_weights) + __ldg(p.weights_offsets + t) + row * D;
+#pragma unroll
+    for (int k = 0; k < kVPL; ++k) {
+      const int vv = k * 32 + v;
+      if (vv < slice_vecs) {
+#pragma unroll
+        for (int e = 0; e < kE; e += 4) update_elems4<WT>(w + vv * kE + e, &acc[k][e], mult);
+      }
+    }
+  }
+}
+
+template <int kE, int kVPL>
+__device__ __forceinline__ void combine_groups(float (&acc)[kVPL][kE], int gs) {
+  for (int o = 16; o >= gs; o >>= 1) {
+#pragma unroll
+    for (int e = 0; e < kE; ++e) acc[0][e] += __shfl_xor_sync(kFullMask, acc[0][e], o);
+  }
+}
+
+struct RunInfo {
+  int t;
+  int64_t row;
+  int D;
+  int slice_vecs;
+  int gs;
+  const char* grad_col;
+  bool ok;  // slice is whole, aligned 16-byte vectors and fits the accumulators
+};
+
+template <typename KeyT, typename GT>
+__device__ __forceinline__ RunInfo describe_run(const BwdDev& p, int64_t s, int max_vpl) {
+  RunInfo r;
+  const int64_t key = static_cast<int64_t>(reinterpret_cast<const KeyT*>(p.sorted_keys)[s]);
+  // table of the key: last t with hash_size_cumsum[t] <= key
+  int lo = 0, hi = p.T - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (__ldg(p.hash_size_cumsum + mid) <= key) {
+      lo = mid;
+    } else {
+      hi = mid - 1;
+    }
+  }
+  r.t = lo;
+  r.row = key - __ldg(p.hash_size_cumsum + lo);
+  const int D_begin = __ldg(p.D_offsets + lo);
+  r.D = __ldg(p.D_offsets + lo + 1) - D_begin;
+  r.slice_vecs = static_cast<int>((static_cast<int64_t>(r.D) * sizeof(GT)) >> 4);
+  r.gs = lanes_per_row(r.slice_vecs);
+  r.grad_col = p.grad_output + (p.grad_col_offset + D_begin) * static_cast<int64_t>(sizeof(GT));
+  r.ok = ((static_cast<int64_t>(r.D) * sizeof(GT)) & 15) == 0 &&
+         (reinterpret_cast<uintptr_t>(r.grad_col) & 15) == 0 && r.slice_vecs <= 32 * max_vpl;
+  if (!r.ok && p.status != nullptr) atomicOr(p.status, B200TBE_DEV_UNSUPPORTED_SHAPE);
+  return r;
+}
+
+// Persistent: warps stride over the runs. Short runs are finished here; long runs are recorded.
+template <typename KeyT, typename WT, typename GT, int kVPL>
+__global__ void __launch_bounds__(kBwdThreads) reduce_runs_kernel(BwdDev p) {
+  constexpr int kE = RowVec<GT>::kElems;
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = static_cast<int64_t>(blockIdx.x) * kBwdWarps + (threadIdx.x >> 5);
+  const int64_t num_warps = static_cast<int64_t>(gridDim.x) * kBwdWarps;
+  const int64_t runs = p.counters[0];
+  for (int64_t run = warp0; run < runs; run += num_warps) {
+    const int64_t s = p.run_start[run], e = p.run_start[run + 1];
+    if (e - s > kLongRun) {
+      const uint32_t chunks = static_cast<uint32_t>((e - s + kLongRun - 1) / kLongRun);
+      uint32_t slot = 0, chunk0 = 0;
+      if (lane == 0) {
+        slot = atomicAdd(p.counters + 1, 1u);
+        chunk0 = atomicAdd(p.counters + 2, chunks);
+        p.long_run[slot] = static_cast<uint32_t>(run);
+        p.long_chunk0[slot] = chunk0;
+      }
+      chunk0 = __shfl_sync(kFullMask, chunk0, 0);
+      slot = __shfl_sync(kFullMask, slot, 0);
+      for (uint32_t c = lane; c < chunks; c += 32) p.chunk_run[chunk0 + c] = slot;
+      continue;
+    }
+    const RunInfo r = describe_run<KeyT, GT>(p, s, kVPL);
+    if (!r.ok) continue;
+    float acc[kVPL][kE];
+#pragma unroll
+    for (int k = 0; k < kVPL; ++k)
+#pragma unroll
+      for (int i = 0; i < kE; ++i) acc[k][i] = 0.f;
+    accumulate_range<GT, kVPL>(p, acc, s, e, r.t, r.gs, r.slice_vecs, r.grad_col, lane);
+    combine_groups<kE, kVPL>(acc, r.gs);
+    apply_update<WT, kE, kVPL>(p, acc, r.t, r.row, r.D, r.gs, r.slice_vecs, lane);
+  }
+}
+
+// Persistent: one warp per chunk of a long run; the chunk's partial row goes to scratch.
+template <typename KeyT, typename GT, int kVPL>
+__global__ void __launch_bounds__(kBwdThreads) reduce_chunks_kernel(BwdDev p) {
+  constexpr int kE = RowVec<GT>::kElems;
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = static_cast<int64_t>(blockIdx.x) * kBwdWarps + (threadIdx.x >> 5);
+  const int64_t num_warps = static_cast<int64_t>(gridDim.x) * kBwdWarps;
+  const int64_t chunks = p.counters[2];
+  for (int64_t c = warp0; c < chunks; c += num_warps) {
+    const uint32_t slot = p.chunk_run[c];
+    const uint32_t run = p.long_run[slot];
+    const int64_t first = p.long_chunk0[slot];
+    const int64_t s_run = p.run_start[run], e_run = p.run_start[run + 1];
+    const int64_t s = s_run + (c - first) * kLongRun;
+    const int64_t e = s + kLongRun < e_run ? s + kLongRun : e_run;
+    const RunInfo r = describe_run<KeyT, GT>(p, s_run, kVPL);
+    if (!r.ok) continue;
+    float acc[kVPL][kE];
+#pragma unroll
+    for (int k = 0; k < kVPL; ++k)
+#pragma unroll
+      for (int i = 0; i < kE; ++i) acc[k][i] = 0.f;
+    accumulate_range<GT, kVPL>(p, acc, s, e, r.t, r.gs, r.slice_vecs, r.grad_col, lane);
+    combine_groups<kE, kVPL>(acc, r.gs);
+    const int g = lane / r.gs, v = lane - g * r.gs;
+    if (g == 0) {
+      float* dst = p.partials + c * p.max_D;
+#pragma unroll
+      for (int k = 0; k < kVPL; ++k) {
+        const int vv = k * 32 + v;
+        if (vv < r.slice_vecs) {
+#pragma unroll
+          for (int i = 0; i < kE; i += 4)
+            *reinterpret_cast<float4*>(dst + vv * kE + i) =
+                make_float4(acc[k][i], acc[k][i + 1], acc[k][i + 2], acc[k][i + 3]);
+        }
+      }
+    }
+  }
+}
+
+// Persistent: one warp per long run adds the run's partial rows in chunk order and updates.
+template <typename KeyT, typename WT, typename GT, int kVPL>
+__global__ void __launch_bounds__(kBwdThreads) finish_long_runs_kernel(BwdDev p) {
+  constexpr int kE = RowVec<GT>::kElems;
+  const int lane = threadIdx.x & 31;
+  const int64_t warp0 = static_cast<int64_t>(blockIdx.x) * kBwdWarps + (threadIdx.x >> 5);
+  const int64_t num_warps = static_cast<int64_t>(gridDim.x) * kBwdWarps;
+  const int64_t long_runs = p.counters[1];
+  for (int64_t i = warp0; i < long_runs; i += num_warps) {
+    const uint32_t run = p.long_run[i];
+    const int64_t s = p.run_start[run], e = p.run_start[run + 1];
+    const int64_t chunks = (e - s + kLongRun - 1) / kLongRun;
+    const RunInfo r = describe_run<KeyT, GT>(p, s, kVPL);
+    if (!r.ok) continue;
+    const int g = lane / r.gs, v = lane - g * r.gs;
+    float acc[kVPL][kE];
+#pragma unroll
+    for (int k = 0; k < kVPL; ++k)
+#pragma unroll
+      for (int j = 0; j < kE; ++j) acc[k][j] = 0.f;
+    if (g == 0) {
+      const float* src = p.partials + static_cast<int64_t>(p.long_chunk0[i]) * p.max_D;
+      for (int64_t c = 0; c < chunks; ++c, src += p.max_D) {
+#pragma unroll
+        for (int k = 0; k < kVPL; ++k) {
+          const int vv = k * 32 + v;
+          if (vv < r.slice_vecs) {
+#pragma unroll
+            for (int j = 0; j < kE; j += 4) {
+              const float4 x = *reinterpret_cast<const float4*>(src + vv * kE + j);
+              acc[k][j] += x.x;
+              acc[k][j + 1] += x.y;
+              acc[k][j + 2] += x.z;
+              acc[k][j + 3] += x.w;
+            }
+          }
+        }
+      }
+    }
+    apply_update<WT, kE, kVPL>(p, acc, r.t, r.row, r.D, r.gs, r.slice_vecs, lane);
+  }
+}
+
+size_t align256(size_t x) { return (x + 255) & ~size_t{255}; }
+
+struct ScratchLayout {
+  size_t keys_a, keys_b, vals_a, vals_b, bag_of_pos, run_start, tile_heads, counters, long_run,
+      long_chunk0, chunk_run, partials, sort, total;
+  int key_bytes;
+  int64_t max_long, max_chunks;
+};
+
+ScratchLayout layout_for(int64_t n, int bits, int max_D) {
+  ScratchLayout L;
+  L.key_bytes = bits <= 32 ? 4 : 8;
+  const size_t nn = static_cast<size_t>(n > 0 ? n : 1);
+  L.max_long = n / kLongRun + 1;
+  L.max_chunks = 2 * (n / kLongRun) + 2;
+  size_t at = 0;
+  auto take = [&](size_t bytes) {
+    const size_t here = at;
+    at += align256(bytes);
+    return here;
+  };
+  L.keys_a = take(nn * L.key_bytes);
+  L.keys_b = take(nn * L.key_bytes);
+  L.vals_a = take(nn * 4);
+  L.vals_b = take(nn * 4);
+  L.bag_of_pos = take(nn * 4);
+  L.run_start = take((nn + 1) * 4);
+  L.tile_heads = take(static_cast<size_t>((n + kSegTile - 1) / kSegTile + 1) * 4);
+  L.counters = take(256);
+  L.long_run = take(static_cast<size_t>(L.max_long) * 4);
+  L.long_chunk0 = take(static_cast<size_t>(L.max_long) * 4);
+  L.chunk_run = take(static_cast<size_t>(L.max_chunks) * 4);
+  L.partials = take(static_cast<size_t>(L.max_chunks) * static_cast<size_t>(max_D > 0 ? max_D : 1) * 4);
+  L.sort = take(radix_sort_scratch_bytes(n));
+  L.total = at;
+  return L;
+}
+
+int persistent_grid() {
+  // one wave of CTAs that all fit at once: 148 SMs x a few CTAs each
+  return kNumSMs * 6;
+}
+
+template <typename KeyT, typename WT, typename GT, int kVPL>
+int run_reduce(const BwdDev& d, cudaStream_t stream) {
+  const int grid = persistent_grid();
+  reduce_runs_kernel<KeyT, WT, GT, kVPL><<<grid, kBwdThreads, 0, stream>>>(d);
+  reduce_chunks_kernel<KeyT, GT, kVPL><<<grid, kBwdThreads, 0, stream>>>(d);
+  finish_long_runs_kernel<KeyT, WT, GT, kVPL><<<grid, kBwdThreads, 0, stream>>>(d);
+  return launch_status();
+}
+
+template <typename KeyT, typename WT, typename GT>
+int dispatch_vpl(const BwdDev& d, int slice_vecs_max, cudaStream_t stream) {
+  if (slice_vecs_max <= 32) return run_reduce<KeyT, WT, GT, 1>(d, stream);
+  if (slice_vecs_max <= 64) return run_reduce<KeyT, WT, GT, 2>(d, stream);
+  if (slice_vecs_max <= 128) return run_reduce<KeyT, WT, GT, 4>(d, stream);
+  if (slice_vecs_max <= 256) return run_reduce<KeyT, WT, GT, 8>(d, stream);
+  return B200TBE_ERR_UNSUPPORTED;
+}
+
+template <typename KeyT, typename IndexT>
+int run_backward(BwdDev d, const b200tbe_backward_params* p, const ScratchLayout& L, char* scratch,
+                 cudaStream_t stream) {
+  const int64_t n = p->num_indices;
+  KeyT* keys_a = reinterpret_cast<KeyT*>(scratch + L.keys_a);
+  KeyT* keys_b = reinterpret_cast<KeyT*>(scratch + L.keys_b);
+  uint32_t* vals_a = reinterpret_cast<uint32_t*>(scratch + L.vals_a);
+  uint32_t* vals_b = reinterpret_cast<uint32_t*>(scratch + L.vals_b);
+  uint32_t* tile_heads = reinterpret_cast<uint32_t*>(scratch + L.tile_heads);
+  const bool weighted = p->per_sample_weights != nullptr;
+
+  if (cudaMemsetAsync(d.counters, 0, 256, stream) != cudaSuccess) return B200TBE_ERR_LAUNCH;
+  const int64_t bags = static_cast<int64_t>(p->T) * p->B;
+  const int64_t lin_ctas = (bags + kBwdWarps - 1) / kBwdWarps;
+  if (lin_ctas > 0x7fffffff) return B200TBE_ERR_TOO_LARGE;
+  if (weighted) {
+    linearize_kernel<KeyT, IndexT, true>
+        <<<static_cast<unsigned>(lin_ctas), kBwdThreads, 0, stream>>>(d, keys_a, vals_a);
+  } else {
+    linearize_kernel<KeyT, IndexT, false>
+        <<<static_cast<unsigned>(lin_ctas), kBwdThreads, 0, stream>>>(d, keys_a, vals_a);
+  }
+  bool in_b = false;
+  int st = radix_sort_pairs(keys_a, vals_a, keys_b, vals_b, n, sizeof(KeyT),
+                            p->total_hash_size_bits, scratch + L.sort,
+                            radix_sort_scratch_bytes(n), &in_b, stream);
+  if (st != B200TBE_OK) return st;
+  const KeyT* keys = in_b ? keys_b : keys_a;
+  d.sorted_keys = keys;
+  d.sorted_vals = in_b ? vals_b : vals_a;
+
+  const int64_t seg_tiles = (n + kSegTile - 1) / kSegTile;
+  count_heads_kernel<KeyT><<<static_cast<unsigned>(seg_tiles), kSegThreads, 0, stream>>>(keys, n, tile_heads);
+  scan_single_cta_kernel<<<1, kScanThreads, 0, stream>>>(tile_heads, seg_tiles, d.counters);
+  write_run_starts_kernel<KeyT><<<static_cast<unsigned>(seg_tiles), kSegThreads, 0, stream>>>(
+      keys, n, tile_heads, d.counters, d.run_start);
+
+  const int grad_bytes = p->grad_dtype == B200TBE_FP32 ? 4 : 2;
+  const int slice_vecs_max = (p->max_D * grad_bytes + 15) / 16;
+  const bool w32 = p->weights_dtype == B200TBE_FP32, g32 = p->grad_dtype == B200TBE_FP32;
+  if (w32 && g32) return dispatch_vpl<KeyT, float, float>(d, slice_vecs_max, stream);
+  if (!w32 && g32) return dispatch_vpl<KeyT, __half, float>(d, slice_vecs_max, stream);
+  if (w32 && !g32) return dispatch_vpl<KeyT, float, __half>(d, slice_vecs_max, stream);
+  return dispatch_vpl<KeyT, __half, __half>(d, slice_vecs_max, stream);
+}
+
+}  // namespace
+}  // namespace b200tbe
+
+using namespace b200tbe;
+
+extern "C" size_t b200tbe_backward_scratch_bytes(int64_t num_indices, int32_t total_hash_size_bits,
+                                                 int32_t max_D) {
+  if (num_indices < 0) return 0;
+  return layout_for(num_indices, total_hash_size_bits, max_D).total;
+}
+
+extern "C" int b200tbe_backward(const b200tbe_backward_params* p, b200tbe_stream_t stream_) {
+  if (p == nullptr) return B200TBE_ERR_BAD_ARG;
+  if (p->T < 0 || p->B < 0 || p->max_D < 0 || p->num_indices < 0) return B200TBE_ERR_BAD_ARG;
+  if (p->T == 0 || p->B == 0 || p->num_indices == 0) return B200TBE_OK;
+  if (p->dev_weights == nullptr || p->weights_offsets == nullptr || p->D_offsets == nullptr ||
+      p->hash_size_cumsum == nullptr || p->indices == nullptr || p->offsets == nullptr ||
+      p->grad_output == nullptr)
+    return B200TBE_ERR_BAD_ARG;
+  if (p->index_bytes != 4 && p->index_bytes != 8) return B200TBE_ERR_BAD_ARG;
+  if (p->optimizer != B200TBE_OPT_SGD && p->optimizer != B200TBE_OPT_ROWWISE_ADAGRAD)
+    return B200TBE_ERR_UNSUPPORTED;
+  if (p->optimizer == B200TBE_OPT_ROWWISE_ADAGRAD &&
+      (p->momentum1 == nullptr || p->momentum1_offsets == nullptr))
+    return B200TBE_ERR_BAD_ARG;
+  if (p->pooling_mode != B200TBE_POOL_SUM && p->pooling_mode != B200TBE_POOL_MEAN)
+    return B200TBE_ERR_UNSUPPORTED;
+  if ((p->weights_dtype != B200TBE_FP32 && p->weights_dtype != B200TBE_FP16) ||
+      (p->grad_dtype != B200TBE_FP32 && p->grad_dtype != B200TBE_FP16))
+    return B200TBE_ERR_UNSUPPORTED;
+  if (p->total_hash_size_bits < 1 || p->total_hash_size_bits > 40) return B200TBE_ERR_UNSUPPORTED;
+  if (p->num_indices >= (int64_t{1} << 31)) return B200TBE_ERR_TOO_LARGE;
+  if (static_cast<int64_t>(p->T) * p->B >= (int64_t{1} << 32) - 1) return B200TBE_ERR_TOO_LARGE;
+  if (p->max_D % 4 != 0) return B200TBE_ERR_UNSUPPORTED;
+  const int grad_bytes = p->grad_dtype == B200TBE_FP32 ? 4 : 2;
+  // gradient slices are read as whole 16-byte vectors
+  if ((p->max_D * grad_bytes) % 16 != 0 || (p->grad_stride * grad_bytes) % 16 != 0 ||
+      (p->grad_col_offset * grad_bytes) % 16 != 0 || !aligned_to(p->grad_output, 16) ||
+      !aligned_to(p->dev_weights, 16))
+    return B200TBE_ERR_UNSUPPORTED;
+  const ScratchLayout L = layout_for(p->num_indices, p->total_hash_size_bits, p->max_D);
+  if (p->scratch == nullptr || p->scratch_bytes < L.total || !aligned_to(p->scratch, 256))
+    return B200TBE_ERR_SCRATCH;
+  char* scratch = static_cast<char*>(p->scratch);
+
+  BwdDev d;
+  d.dev_weights = static_cast<char*>(p->dev_weights);
+  d.weights_offsets = p->weights_offsets;
+  d.D_offsets = p->D_offsets;
+  d.hash_size_cumsum = p->hash_size_cumsum;
+  d.indices = p->indices;
+  d.offsets = p->offsets;
+  d.per_sample_weights = p->per_sample_weights;
+  d.grad_output = static_cast<const char*>(p->grad_output);
+  d.grad_stride = p->grad_stride;
+  d.grad_col_offset = p->grad_col_offset;
+  d.momentum1 = p->momentum1;
+  d.momentum1_offsets = p->momentum1_offsets;
+  d.num_indices = p->num_indices;
+  d.T = p->T;
+  d.B = p->B;
+  d.pooling_mode = p->pooling_mode;
+  d.optimizer = p->optimizer;
+  d.index_bytes = p->index_bytes;
+  d.learning_rate = p->learning_rate;
+  d.eps = p->eps;
+  d.status = p->status;
+  d.sorted_keys = nullptr;
+  d.sorted_vals = nullptr;
+  d.bag_of_pos = reinterpret_cast<uint32_t*>(scratch + L.bag_of_pos);
+  d.run_start = reinterpret_cast<uint32_t*>(scratch + L.run_start);
+  d.counters = reinterpret_cast<uint32_t*>(scratch + L.counters);
+  d.long_run = reinterpret_cast<uint32_t*>(scratch + L.long_run);
+  d.long_chunk0 = reinterpret_cast<uint32_t*>(scratch + L.long_chunk0);
+  d.chunk_run = reinterpret_cast<uint32_t*>(scratch + L.chunk_run);
+  d.partials = reinterpret_cast<float*>(scratch + L.partials);
+  d.max_D = p->max_D;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  const bool k32 = L.key_bytes == 4, i64 = p->index_bytes == 8;
+  if (k32) {
+    return i64 ? run_backward<uint32_t, int64_t>(d, p, L, scratch, stream)
+               : run_backward<uint32_t, int32_t>(d, p, L, scratch, stream);
+  }
+  return i64 ? run_backward<unsigned long long, int64_t>(d, p, L, scratch, stream)
+             : run_backward<unsigned long long, int32_t>(d, p, L, scratch, stream);
+}
