@@ -266,7 +266,8 @@ def reference_arm(args, cfg, rank):
 # --------------------------------------------------------------------------------------------
 # The other named configurations, single GPU, one kernel (or kernel group) each
 # --------------------------------------------------------------------------------------------
-def bench_others(peak_gbs, iters=20):
+def bench_others(peak_gbs, iters=20, only=None):
+    """only: None (all), or one of 'jagged', 'fp32', 'train', 'nbit'."""
     res = {}
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device="cuda")
     gen = torch.Generator(device="cuda").manual_seed(99)
@@ -280,6 +281,8 @@ def bench_others(peak_gbs, iters=20):
             e.update(extra)
         res[name] = e
 
+    if only not in (None, "jagged"):
+        return _others_tbe(res, entry, flush, gen, iters, only)
     # config 2: jagged ops
     c = workloads.CONFIGS["jagged"]
     j = workloads.jagged_inputs(c["B"], c["max_L"], c["D"], c["seed"])
@@ -295,7 +298,22 @@ def bench_others(peak_gbs, iters=20):
     ms, _ = time_launches(lambda: cabi.jagged_dense_elementwise_add(values, [off], y), iters, flush)
     entry("jagged_dense_elementwise_add", j.total_rows * row + 2 * j.B * j.max_L * row + (j.B + 1) * 8, ms)
     del values, y, dense
+    if only == "jagged":
+        return res
+    return _others_tbe(res, entry, flush, gen, iters, only)
 
+
+def _others_tbe(res, entry, flush, gen, iters, only):
+    if only in (None, "fp32"):
+        _bench_fp32(entry, flush, gen, iters)
+    if only in (None, "train"):
+        _bench_train(entry, flush, gen, iters)
+    if only in (None, "nbit"):
+        _bench_nbit(entry, flush, gen, iters)
+    return res
+
+
+def _bench_fp32(entry, flush, gen, iters):
     # config 1: fp32 forward, uniform ids
     c = workloads.CONFIGS["tbe_fp32_fwd"]
     inp = workloads.tbe_inputs(c["T"], c["B"], c["E"], c["D"], c["L_lo"], c["L_hi"], c["seed"], c["dist"])
@@ -311,8 +329,9 @@ def bench_others(peak_gbs, iters=20):
     ms, _ = time_launches(fn, iters, flush)
     entry("tbe_fp32_forward(config1)", workloads.forward_bytes(inp.num_lookups, inp.unique_rows(), D * 4, T, B, D, 4),
           ms, inp.num_lookups)
-    del W, out
 
+
+def _bench_train(entry, flush, gen, iters):
     # config 3: fp16 tables, forward and backward + Adagrad
     c = workloads.CONFIGS["tbe_fp16_train"]
     T, E, D, B = c["T"], c["E"], c["D"], c["B"]
@@ -339,8 +358,9 @@ def bench_others(peak_gbs, iters=20):
     ms, _ = time_launches(bwd, iters, flush)
     entry("tbe_fp16_backward_adagrad(config3)", workloads.backward_bytes(inp.num_lookups, U, D * 2, T, B, D, 4),
           ms, inp.num_lookups, {"kernels_per_call": backward_launches(bits)})
-    del W, mom, out, grad, scratch
 
+
+def _bench_nbit(entry, flush, gen, iters):
     # config 4: quantised inference forward, half INT8 / half INT4 tables
     c = workloads.CONFIGS["tbe_nbit_fwd"]
     T, E, D, B = c["T"], c["E"], c["D"], c["B"]
@@ -373,7 +393,6 @@ def bench_others(peak_gbs, iters=20):
     ms, _ = time_launches(fn, max(5, iters // 2), flush)
     bytes_ = row_bytes + inp.num_lookups * 8 + (T * B + 1) * 8 + B * T * D * 2
     entry("tbe_nbit_forward(config4)", bytes_, ms, inp.num_lookups, {"unique_rows": int(sum(U_by_table))})
-    return res
 
 
 def main():
@@ -384,6 +403,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-others", action="store_true", help="skip the single-kernel configurations")
     ap.add_argument("--small", action="store_true", help="tiny tables, for profiler captures and smoke runs")
+    ap.add_argument("--only", default=None, choices=["jagged", "fp32", "train", "nbit"],
+                    help="run one single-GPU configuration alone (few launches; for profiler captures)")
+    ap.add_argument("--iters", type=int, default=20, help="timed launches per single-GPU configuration")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" and not args.small else args.warmup
 
@@ -406,6 +428,10 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     cabi.lib()
     peak_gbs, peak_kind = measured_peak_gbs()
+    if args.only is not None:
+        print(json.dumps({"only": args.only, "peak_gbs": peak_gbs,
+                          "results": bench_others(peak_gbs, args.iters, args.only)}))
+        return
 
     step = ShardedTbeStep(rank, world, cfg, small=args.small)
 

@@ -398,7 +398,8 @@ Tensor split_embedding_codegen_lookup_sgd_function(
                                   total_hash_size_bits, indices, offsets, pooling_mode,
                                   indice_weights, output_dtype,
                                   static_cast<int64_t>(B200TBE_OPT_SGD), learning_rate, 0.0,
-                                  Tensor(), Tensor());
+                                  at::empty({0}, dev_weights.options().dtype(at::kFloat)),
+                                  at::empty({0}, dev_weights.options().dtype(at::kLong)));
 }
 
 // ---- quantised inference lookup ----------------------------------------------------------------
