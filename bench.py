@@ -29,6 +29,7 @@ if ROOT not in sys.path:
 from torchlib_xpu_b200 import cabi, workloads  # noqa: E402
 
 L2_FLUSH_BYTES = 512 << 20
+TABLES_OVERRIDE = None   # --tables: fewer tables for --only runs (small profiler captures)
 
 
 def measured_peak_gbs():
@@ -334,7 +335,7 @@ def _bench_fp32(entry, flush, gen, iters):
 def _bench_train(entry, flush, gen, iters):
     # config 3: fp16 tables, forward and backward + Adagrad
     c = workloads.CONFIGS["tbe_fp16_train"]
-    T, E, D, B = c["T"], c["E"], c["D"], c["B"]
+    T, E, D, B = TABLES_OVERRIDE or c["T"], c["E"], c["D"], c["B"]
     inp = workloads.tbe_inputs(T, B, E, D, c["L_lo"], c["L_hi"], c["seed"], "zipf", c["alpha"], c["permute"])
     U = inp.unique_rows()
     W = uniform_half_table(T * E * D, -0.01, 0.01, gen)
@@ -363,7 +364,7 @@ def _bench_train(entry, flush, gen, iters):
 def _bench_nbit(entry, flush, gen, iters):
     # config 4: quantised inference forward, half INT8 / half INT4 tables
     c = workloads.CONFIGS["tbe_nbit_fwd"]
-    T, E, D, B = c["T"], c["E"], c["D"], c["B"]
+    T, E, D, B = TABLES_OVERRIDE or c["T"], c["E"], c["D"], c["B"]
     inp = workloads.tbe_inputs(T, B, E, D, c["L_lo"], c["L_hi"], c["seed"], "zipf", c["alpha"])
     U_by_table = []
     strides = [144 if t < T // 2 else 80 for t in range(T)]
@@ -406,6 +407,8 @@ def main():
     ap.add_argument("--only", default=None, choices=["jagged", "fp32", "train", "nbit"],
                     help="run one single-GPU configuration alone (few launches; for profiler captures)")
     ap.add_argument("--iters", type=int, default=20, help="timed launches per single-GPU configuration")
+    ap.add_argument("--tables", type=int, default=None,
+                    help="with --only train|nbit: use this many tables (a small case for profiler captures)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" and not args.small else args.warmup
 
@@ -429,6 +432,8 @@ def main():
     cabi.lib()
     peak_gbs, peak_kind = measured_peak_gbs()
     if args.only is not None:
+        global TABLES_OVERRIDE
+        TABLES_OVERRIDE = args.tables
         print(json.dumps({"only": args.only, "peak_gbs": peak_gbs,
                           "results": bench_others(peak_gbs, args.iters, args.only)}))
         return

@@ -63,6 +63,7 @@ typedef enum { B200TBE_OPT_SGD = 0, B200TBE_OPT_ROWWISE_ADAGRAD = 1 } b200tbe_op
 #define B200TBE_DEV_INDEX_OUT_OF_RANGE 1
 #define B200TBE_DEV_OFFSETS_NOT_MONOTONE 2
 #define B200TBE_DEV_UNSUPPORTED_SHAPE 4 /* a table's row is not whole 16-byte vectors */
+#define B200TBE_DEV_WAIT_TIMEOUT 8      /* a bounded wait inside a kernel gave up */
 
 #define B200TBE_MAX_DESTS 16
 #define B200TBE_MAX_JAGGED_DIMS 4

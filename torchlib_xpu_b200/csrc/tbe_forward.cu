@@ -1,24 +1,10 @@
-// TBE pooled forward over fp32 / fp16 tables: one warp per bag.
-//
-// A row of D elements is D*sizeof(W)/16 16-byte vectors. When that is fewer than 32 the warp splits
-// into 32/gs groups of gs lanes (gs = the vector count rounded up to a power of two) and each group
-// fetches a different row of the bag with the same load instruction, so every lane always issues a
-// full 16-byte load: D=128 fp32 -> 32 lanes x 16 B = one 512-byte row per instruction, D=128 fp16
-// -> two 256-byte rows per instruction. The bag's indices are fetched 32 at a time with one
-// coalesced load and handed out by shuffle. kUnroll row loads are issued back to back before any
-// of them is consumed, which is what keeps enough bytes in flight to cover HBM latency. The
-// accumulators are fp32 registers; groups are combined by shuffle at the end and group 0 writes the
-// pooled vector. Bags are table-major, so concurrently running CTAs work on the same table and
-// rows that repeat across bags (Zipf-distributed ids) are served by L2.
-#include "tbe_pool.cuh"
+// TBE pooled forward over fp32 / fp16 tables, on the streaming gather engine of tbe_stream.cuh.
+#include "tbe_stream.cuh"
 
 namespace b200tbe {
 namespace {
 
-constexpr int kFwdWarps = 8;
-constexpr int kFwdThreads = kFwdWarps * kWarpSize;
-
-struct FwdDev {
+struct FwdParams {
   const char* dev_weights;
   const int64_t* weights_offsets;
   const int32_t* D_offsets;
@@ -34,121 +20,78 @@ struct FwdDev {
   int32_t B;
   int32_t pooling_mode;
   int32_t* status;
+  int32_t bags_per_unit;
+  int32_t units_per_table;
+  int64_t num_units;
 };
 
-// kVPL = 16-byte vectors per lane a row may need (rows of up to 32*kVPL vectors).
+// kVPL: vectors of 4 elements a lane may hold (rows of up to 128 * kVPL elements).
 template <typename WT, typename OT, typename IndexT, int kVPL>
-__global__ void __launch_bounds__(kFwdThreads) tbe_forward_kernel(FwdDev p) {
-  constexpr int kE = RowVec<WT>::kElems;
-  constexpr int kUnroll = kVPL == 1 ? 4 : (kVPL == 2 ? 2 : 1);
-  const int lane = threadIdx.x & 31;
-  const int64_t bag =
-      static_cast<int64_t>(blockIdx.x) * kFwdWarps + (threadIdx.x >> 5);
-  if (bag >= static_cast<int64_t>(p.T) * p.B) return;
-  const int t = static_cast<int>(bag / p.B);
-  const int b = static_cast<int>(bag - static_cast<int64_t>(t) * p.B);
-
-  const int D_begin = __ldg(p.D_offsets + t);
-  const int D = __ldg(p.D_offsets + t + 1) - D_begin;
-  const int64_t row_bytes = static_cast<int64_t>(D) * sizeof(WT);
-  const char* table = p.dev_weights + __ldg(p.weights_offsets + t) * static_cast<int64_t>(sizeof(WT));
-  const int64_t num_rows = p.rows_per_table ? __ldg(p.rows_per_table + t) : -1;
-  const int64_t start = load_index<IndexT>(p.offsets, bag);
-  const int64_t end = load_index<IndexT>(p.offsets, bag + 1);
-
-  const int dest = static_cast<int>(b / p.rows_per_dest);
-  const int64_t dest_row = b - dest * p.rows_per_dest;
-  OT* out = static_cast<OT*>(p.outputs[dest]) + dest_row * p.output_stride + p.output_col_offset +
-            D_begin;
-
-  float acc[kVPL][kE];
-#pragma unroll
-  for (int k = 0; k < kVPL; ++k)
-#pragma unroll
-    for (int e = 0; e < kE; ++e) acc[k][e] = 0.f;
-
-  const bool weighted = p.per_sample_weights != nullptr;
-  const bool vector_rows = (row_bytes & 15) == 0 && (reinterpret_cast<uintptr_t>(table) & 15) == 0;
-
-  if (vector_rows) {
-    const int row_vecs = static_cast<int>(row_bytes >> 4);
-    const int gs = lanes_per_row(row_vecs);
-    const int g = lane / gs;
-    const int v = lane - g * gs;
-    pool_vector_rows<WT, IndexT, kVPL, kUnroll>(acc, table, row_bytes, row_vecs, gs, p.indices,
-                                                p.per_sample_weights, start, end, num_rows,
-                                                p.status, lane);
-    // combine the groups (gs < 32 implies a single vector per lane)
-    for (int o = 16; o >= gs; o >>= 1) {
-#pragma unroll
-      for (int e = 0; e < kE; ++e) acc[0][e] += __shfl_xor_sync(kFullMask, acc[0][e], o);
-    }
-    float scale = 1.f;
-    if (p.pooling_mode == B200TBE_POOL_MEAN && end > start) scale = 1.f / static_cast<float>(end - start);
-    if (g == 0) {
-#pragma unroll
-      for (int k = 0; k < kVPL; ++k) {
-        const int vv = k * 32 + v;
-        if (vv < row_vecs) {
-          float r[kE];
-#pragma unroll
-          for (int e = 0; e < kE; ++e) r[e] = acc[k][e] * scale;
-          store_pooled<OT, kE>(out + vv * kE, r);
-        }
-      }
-    }
-  } else {
-    // Rows that are not whole 16-byte vectors: element e of the row lives in lane e % 32.
-    float* facc = &acc[0][0];
-    for (int64_t c = start; c < end; ++c) {
-      const int64_t idx = load_index<IndexT>(p.indices, c);
-      const float w = weighted ? __ldg(p.per_sample_weights + c) : 1.f;
-      if (num_rows >= 0 && (idx < 0 || idx >= num_rows)) {
-        if (lane == 0) atomicOr(p.status, B200TBE_DEV_INDEX_OUT_OF_RANGE);
-        continue;
-      }
-      const char* row = table + idx * row_bytes;
-#pragma unroll
-      for (int i = 0; i < kVPL * kE; ++i) {
-        const int e = i * 32 + lane;
-        if (e < D) facc[i] = fmaf(RowVec<WT>::scalar(row + e * sizeof(WT)), w, facc[i]);
-      }
-    }
-    float scale = 1.f;
-    if (p.pooling_mode == B200TBE_POOL_MEAN && end > start) scale = 1.f / static_cast<float>(end - start);
-#pragma unroll
-    for (int i = 0; i < kVPL * kE; ++i) {
-      const int e = i * 32 + lane;
-      if (e < D) out[e] = to_out(facc[i] * scale, static_cast<OT*>(nullptr));
+__global__ void __launch_bounds__(kStreamThreads, 1)
+    tbe_forward_kernel(const __grid_constant__ FwdParams p) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  WarpRing* rings = reinterpret_cast<WarpRing*>(smem_raw);
+  stream_init_rings(rings);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  WarpRing& ring = rings[warp];
+  uint32_t phases = 0;
+  const StreamBags bags{p.indices, p.offsets, p.per_sample_weights, p.status, p.pooling_mode};
+  const int64_t stride_units = static_cast<int64_t>(gridDim.x) * kStreamWarps;
+  for (int64_t unit = static_cast<int64_t>(blockIdx.x) * kStreamWarps + warp; unit < p.num_units;
+       unit += stride_units) {
+    const int t = static_cast<int>(unit / p.units_per_table);
+    const int b0 = static_cast<int>(unit - static_cast<int64_t>(t) * p.units_per_table) * p.bags_per_unit;
+    const int nb = p.B - b0 < p.bags_per_unit ? p.B - b0 : p.bags_per_unit;
+    const int D_begin = __ldg(p.D_offsets + t);
+    const int D = __ldg(p.D_offsets + t + 1) - D_begin;
+    const int64_t row_bytes = static_cast<int64_t>(D) * sizeof(WT);
+    const char* table = p.dev_weights + __ldg(p.weights_offsets + t) * static_cast<int64_t>(sizeof(WT));
+    const int64_t num_rows = p.rows_per_table ? __ldg(p.rows_per_table + t) : -1;
+    const int64_t bag0 = static_cast<int64_t>(t) * p.B + b0;
+    const int64_t col = p.output_col_offset + D_begin;
+    OT* const* outputs = reinterpret_cast<OT* const*>(p.outputs);
+    const bool streamable = (D & 3) == 0 && (row_bytes & 15) == 0 &&
+                            (reinterpret_cast<uintptr_t>(table) & 15) == 0 &&
+                            row_bytes <= kStageBytes && (D >> 2) <= 32 * kVPL && D > 0;
+    if (streamable) {
+      const StreamTable tab{table, row_bytes, static_cast<int>(row_bytes), D >> 2, num_rows};
+      const StreamOut<OT> out{outputs, p.output_stride, col, p.rows_per_dest};
+      if (!stream_unit<FloatRow<WT>, OT, IndexT, kVPL>(bags, tab, out, bag0, b0, nb, ring, phases, lane))
+        return;
+    } else {
+      pool_unit_generic<OT, IndexT>(p.indices, p.offsets, p.per_sample_weights, p.status,
+                                    p.pooling_mode, sizeof(WT) == 4 ? B200TBE_FP32 : B200TBE_FP16,
+                                    table, row_bytes, D, num_rows, outputs, p.output_stride, col,
+                                    p.rows_per_dest, bag0, b0, nb, lane);
     }
   }
 }
 
-template <typename WT, typename OT, typename IndexT>
-int launch_forward(const FwdDev& d, int64_t max_row_bytes, cudaStream_t stream) {
-  const int64_t bags = static_cast<int64_t>(d.T) * d.B;
-  const int64_t ctas = (bags + kFwdWarps - 1) / kFwdWarps;
-  if (ctas > 0x7fffffff) return B200TBE_ERR_TOO_LARGE;
-  const unsigned grid = static_cast<unsigned>(ctas);
-  const int64_t vecs = (max_row_bytes + 15) / 16;
-  if (vecs <= 32) {
-    tbe_forward_kernel<WT, OT, IndexT, 1><<<grid, kFwdThreads, 0, stream>>>(d);
-  } else if (vecs <= 64) {
-    tbe_forward_kernel<WT, OT, IndexT, 2><<<grid, kFwdThreads, 0, stream>>>(d);
-  } else if (vecs <= 128) {
-    tbe_forward_kernel<WT, OT, IndexT, 4><<<grid, kFwdThreads, 0, stream>>>(d);
-  } else if (vecs <= 256) {
-    tbe_forward_kernel<WT, OT, IndexT, 8><<<grid, kFwdThreads, 0, stream>>>(d);
-  } else {
-    return B200TBE_ERR_UNSUPPORTED;
-  }
+template <typename WT, typename OT, typename IndexT, int kVPL>
+int launch_one(const FwdParams& d, cudaStream_t stream) {
+  auto kernel = tbe_forward_kernel<WT, OT, IndexT, kVPL>;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(kStreamSmemBytes)) != cudaSuccess)
+    return B200TBE_ERR_LAUNCH;
+  const int64_t ctas = (d.num_units + kStreamWarps - 1) / kStreamWarps;
+  const unsigned grid = static_cast<unsigned>(ctas < kNumSMs ? ctas : kNumSMs);
+  kernel<<<grid, kStreamThreads, kStreamSmemBytes, stream>>>(d);
   return launch_status();
 }
 
+template <typename WT, typename OT, typename IndexT>
+int launch_forward(const FwdParams& d, int max_D, cudaStream_t stream) {
+  if (max_D <= 128) return launch_one<WT, OT, IndexT, 1>(d, stream);
+  if (max_D <= 256) return launch_one<WT, OT, IndexT, 2>(d, stream);
+  if (max_D <= 512) return launch_one<WT, OT, IndexT, 4>(d, stream);
+  if (max_D <= 1024) return launch_one<WT, OT, IndexT, 8>(d, stream);
+  return B200TBE_ERR_UNSUPPORTED;
+}
+
 template <typename WT, typename OT>
-int dispatch_index(const FwdDev& d, int64_t max_row_bytes, int index_bytes, cudaStream_t stream) {
-  if (index_bytes == 8) return launch_forward<WT, OT, int64_t>(d, max_row_bytes, stream);
-  return launch_forward<WT, OT, int32_t>(d, max_row_bytes, stream);
+int dispatch_index(const FwdParams& d, int max_D, int index_bytes, cudaStream_t stream) {
+  if (index_bytes == 8) return launch_forward<WT, OT, int64_t>(d, max_D, stream);
+  return launch_forward<WT, OT, int32_t>(d, max_D, stream);
 }
 
 }  // namespace
@@ -169,7 +112,7 @@ extern "C" int b200tbe_forward(const b200tbe_forward_params* p, b200tbe_stream_t
   if (p->rows_per_table != nullptr && p->status == nullptr) return B200TBE_ERR_BAD_ARG;
   if (p->pooling_mode != B200TBE_POOL_SUM && p->pooling_mode != B200TBE_POOL_MEAN)
     return B200TBE_ERR_UNSUPPORTED;
-  FwdDev d;
+  FwdParams d;
   d.dev_weights = static_cast<const char*>(p->dev_weights);
   d.weights_offsets = p->weights_offsets;
   d.D_offsets = p->D_offsets;
@@ -188,15 +131,18 @@ extern "C" int b200tbe_forward(const b200tbe_forward_params* p, b200tbe_stream_t
   d.B = p->B;
   d.pooling_mode = p->pooling_mode;
   d.status = p->status;
+  d.bags_per_unit = stream_bags_per_unit(p->T, p->B);
+  d.units_per_table = (p->B + d.bags_per_unit - 1) / d.bags_per_unit;
+  d.num_units = static_cast<int64_t>(p->T) * d.units_per_table;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   const int w = p->weights_dtype, o = p->output_dtype;
   if (w == B200TBE_FP32 && o == B200TBE_FP32)
-    return dispatch_index<float, float>(d, int64_t{p->max_D} * 4, p->index_bytes, stream);
+    return dispatch_index<float, float>(d, p->max_D, p->index_bytes, stream);
   if (w == B200TBE_FP32 && o == B200TBE_FP16)
-    return dispatch_index<float, __half>(d, int64_t{p->max_D} * 4, p->index_bytes, stream);
+    return dispatch_index<float, __half>(d, p->max_D, p->index_bytes, stream);
   if (w == B200TBE_FP16 && o == B200TBE_FP32)
-    return dispatch_index<__half, float>(d, int64_t{p->max_D} * 2, p->index_bytes, stream);
+    return dispatch_index<__half, float>(d, p->max_D, p->index_bytes, stream);
   if (w == B200TBE_FP16 && o == B200TBE_FP16)
-    return dispatch_index<__half, __half>(d, int64_t{p->max_D} * 2, p->index_bytes, stream);
+    return dispatch_index<__half, __half>(d, p->max_D, p->index_bytes, stream);
   return B200TBE_ERR_UNSUPPORTED;
 }
