@@ -34,6 +34,7 @@ constexpr int kWaitSpins = 1 << 22;  // bounded mbarrier wait (each try blocks f
 struct WarpRing {
   alignas(128) char rows[kStages][kStageBytes];
   float weights[kStages][32];
+  float2 mult[kStages][32];   // per row {multiplier, bias term} of the stage being consumed
   uint32_t valid[kStages];
   uint32_t pad_;
   unsigned long long bar[kStages];
@@ -110,9 +111,51 @@ struct StreamBags {
   int pooling_mode;
 };
 
-// ---- row readers: 4 elements (vector v) of a row that sits in shared memory -------------------
-struct RowHeader {
-  float scale, bias;
+// ---- shared-memory loads by 32-bit shared address ------------------------------------------------
+__device__ __forceinline__ uint32_t lds_u8(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u8 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_u16(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds_u32(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint2 lds_u64(uint32_t a) {
+  uint2 v;
+  asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint4 lds_u128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(a));
+  return v;
+}
+__device__ __forceinline__ float2 lds_f32x2(uint32_t a) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a));
+  return v;
+}
+
+// ---- row readers ----------------------------------------------------------------------------------
+// A reader turns vector v (elements [4v, 4v+4)) of a row in shared memory into two float2 and adds
+// them, scaled by sw, to two float2 accumulators. Quantised readers build floats with the
+// "magic number" trick: OR-ing a small integer into the mantissa of 2^23 gives 2^23 + q exactly, a
+// subtraction gives q -- logic and FMA-pipe instructions only, no int-to-float conversions, and the
+// packed f32x2 instructions of sm_100 halve the arithmetic instruction count.
+constexpr uint32_t kMagicBits = 0x4B000000u;  // 2^23
+constexpr float kMagic = 8388608.f;
+
+struct Acc4 {
+  float2 lo, hi;
 };
 
 template <typename WT>
@@ -120,19 +163,33 @@ struct FloatRow;
 template <>
 struct FloatRow<float> {
   static constexpr bool kHasHeader = false;
-  static __device__ __forceinline__ RowHeader header(const char*) { return {1.f, 0.f}; }
-  static __device__ __forceinline__ float4 load4(const char* row, int v) {
-    return *reinterpret_cast<const float4*>(row + (v << 4));
+  static constexpr int kHeaderBytes = 0;
+  static __device__ __forceinline__ void add(Acc4& a, uint32_t row, int v) {
+    const uint4 x = lds_u128(row + (v << 4));
+    a.lo = __fadd2_rn(a.lo, make_float2(__uint_as_float(x.x), __uint_as_float(x.y)));
+    a.hi = __fadd2_rn(a.hi, make_float2(__uint_as_float(x.z), __uint_as_float(x.w)));
+  }
+  static __device__ __forceinline__ void fma(Acc4& a, uint32_t row, int v, float sw) {
+    const uint4 x = lds_u128(row + (v << 4));
+    const float2 s = make_float2(sw, sw);
+    a.lo = __ffma2_rn(make_float2(__uint_as_float(x.x), __uint_as_float(x.y)), s, a.lo);
+    a.hi = __ffma2_rn(make_float2(__uint_as_float(x.z), __uint_as_float(x.w)), s, a.hi);
   }
 };
 template <>
 struct FloatRow<__half> {
   static constexpr bool kHasHeader = false;
-  static __device__ __forceinline__ RowHeader header(const char*) { return {1.f, 0.f}; }
-  static __device__ __forceinline__ float4 load4(const char* row, int v) {
-    const uint2 raw = *reinterpret_cast<const uint2*>(row + (v << 3));
-    const float2 a = half2_bits_to_float2(raw.x), b = half2_bits_to_float2(raw.y);
-    return make_float4(a.x, a.y, b.x, b.y);
+  static constexpr int kHeaderBytes = 0;
+  static __device__ __forceinline__ void add(Acc4& a, uint32_t row, int v) {
+    const uint2 x = lds_u64(row + (v << 3));
+    a.lo = __fadd2_rn(a.lo, half2_bits_to_float2(x.x));
+    a.hi = __fadd2_rn(a.hi, half2_bits_to_float2(x.y));
+  }
+  static __device__ __forceinline__ void fma(Acc4& a, uint32_t row, int v, float sw) {
+    const uint2 x = lds_u64(row + (v << 3));
+    const float2 s = make_float2(sw, sw);
+    a.lo = __ffma2_rn(half2_bits_to_float2(x.x), s, a.lo);
+    a.hi = __ffma2_rn(half2_bits_to_float2(x.y), s, a.hi);
   }
 };
 
@@ -141,38 +198,48 @@ struct QuantRow;
 template <>
 struct QuantRow<8> {
   static constexpr bool kHasHeader = true;
-  static __device__ __forceinline__ RowHeader header(const char* row) {
-    const float2 sb = half2_bits_to_float2(*reinterpret_cast<const uint32_t*>(row));
-    return {sb.x, sb.y};
-  }
-  static __device__ __forceinline__ float4 load4(const char* row, int v) {
-    const uint32_t w = *reinterpret_cast<const uint32_t*>(row + 4 + (v << 2));
-    return make_float4(static_cast<float>(w & 0xffu), static_cast<float>((w >> 8) & 0xffu),
-                       static_cast<float>((w >> 16) & 0xffu), static_cast<float>(w >> 24));
+  static constexpr int kHeaderBytes = 4;
+  static __device__ __forceinline__ void fma(Acc4& a, uint32_t row, int v, float sw) {
+    const uint32_t w = lds_u32(row + 4 + (v << 2));
+    const float2 neg = make_float2(-kMagic, -kMagic), s = make_float2(sw, sw);
+    const float2 q01 = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(w, kMagicBits, 0x7440)),
+                                              __uint_as_float(__byte_perm(w, kMagicBits, 0x7441))), neg);
+    const float2 q23 = __fadd2_rn(make_float2(__uint_as_float(__byte_perm(w, kMagicBits, 0x7442)),
+                                              __uint_as_float(__byte_perm(w, kMagicBits, 0x7443))), neg);
+    a.lo = __ffma2_rn(q01, s, a.lo);
+    a.hi = __ffma2_rn(q23, s, a.hi);
   }
 };
 template <>
 struct QuantRow<4> {
   static constexpr bool kHasHeader = true;
-  static __device__ __forceinline__ RowHeader header(const char* row) {
-    return QuantRow<8>::header(row);
-  }
-  static __device__ __forceinline__ float4 load4(const char* row, int v) {
-    const uint32_t w = *reinterpret_cast<const unsigned short*>(row + 4 + (v << 1));
-    return make_float4(static_cast<float>(w & 0xfu), static_cast<float>((w >> 4) & 0xfu),
-                       static_cast<float>((w >> 8) & 0xfu), static_cast<float>(w >> 12));
+  static constexpr int kHeaderBytes = 4;
+  static __device__ __forceinline__ void fma(Acc4& a, uint32_t row, int v, float sw) {
+    // nibble k stays at bit 4k inside the mantissa: the float is 2^23 + 16^k * q, and the factor
+    // 16^-k (a power of two, exact) goes into the multiplier
+    const uint32_t w = lds_u16(row + 4 + (v << 1));
+    const float2 neg = make_float2(-kMagic, -kMagic);
+    const float2 q01 = __fadd2_rn(make_float2(__uint_as_float((w & 0x000fu) | kMagicBits),
+                                              __uint_as_float((w & 0x00f0u) | kMagicBits)), neg);
+    const float2 q23 = __fadd2_rn(make_float2(__uint_as_float((w & 0x0f00u) | kMagicBits),
+                                              __uint_as_float((w & 0xf000u) | kMagicBits)), neg);
+    a.lo = __ffma2_rn(q01, make_float2(sw, sw * 0.0625f), a.lo);
+    a.hi = __ffma2_rn(q23, make_float2(sw * (1.f / 256.f), sw * (1.f / 4096.f)), a.hi);
   }
 };
 template <>
 struct QuantRow<2> {
   static constexpr bool kHasHeader = true;
-  static __device__ __forceinline__ RowHeader header(const char* row) {
-    return QuantRow<8>::header(row);
-  }
-  static __device__ __forceinline__ float4 load4(const char* row, int v) {
-    const uint32_t w = *reinterpret_cast<const unsigned char*>(row + 4 + v);
-    return make_float4(static_cast<float>(w & 0x3u), static_cast<float>((w >> 2) & 0x3u),
-                       static_cast<float>((w >> 4) & 0x3u), static_cast<float>(w >> 6));
+  static constexpr int kHeaderBytes = 4;
+  static __device__ __forceinline__ void fma(Acc4& a, uint32_t row, int v, float sw) {
+    const uint32_t w = lds_u8(row + 4 + v);
+    const float2 neg = make_float2(-kMagic, -kMagic);
+    const float2 q01 = __fadd2_rn(make_float2(__uint_as_float((w & 0x03u) | kMagicBits),
+                                              __uint_as_float((w & 0x0cu) | kMagicBits)), neg);
+    const float2 q23 = __fadd2_rn(make_float2(__uint_as_float((w & 0x30u) | kMagicBits),
+                                              __uint_as_float((w & 0xc0u) | kMagicBits)), neg);
+    a.lo = __ffma2_rn(q01, make_float2(sw, sw * 0.25f), a.lo);
+    a.hi = __ffma2_rn(q23, make_float2(sw * 0.0625f, sw * (1.f / 64.f)), a.hi);
   }
 };
 
@@ -183,6 +250,84 @@ struct StreamOut {
   int64_t output_stride;
   int64_t col;                // output_col_offset + D_offsets[t]
   int64_t rows_per_dest;
+};
+
+// n consecutive rows, all valid, no bag boundary inside. kScaled: every row has a {multiplier, bias
+// term} pair in the stage's side table (quantised rows and/or per-sample weights).
+template <typename Row, int kVPL, bool kScaled>
+__device__ __forceinline__ void consume_rows(Acc4 (&acc)[kVPL], float& bias_acc, uint32_t row,
+                                             uint32_t mult, int copy_bytes, int n, int nvec,
+                                             int lane) {
+  constexpr int kU = kVPL == 1 ? 4 : (kVPL == 2 ? 2 : 1);
+  int i = 0;
+  for (; i + kU <= n; i += kU) {
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      float sw = 1.f;
+      if (kScaled) {
+        const float2 m = lds_f32x2(mult + 8 * u);
+        sw = m.x;
+        bias_acc += m.y;
+      }
+#pragma unroll
+      for (int k = 0; k < kVPL; ++k) {
+        const int v = k * 32 + lane;
+        if (kVPL == 1 || v < nvec) {
+          if constexpr (kScaled) {
+            Row::fma(acc[k], row + u * copy_bytes, v, sw);
+          } else {
+            Row::add(acc[k], row + u * copy_bytes, v);
+          }
+        }
+      }
+    }
+    row += kU * copy_bytes;
+    mult += kU * 8;
+  }
+  for (; i < n; ++i) {
+    float sw = 1.f;
+    if (kScaled) {
+      const float2 m = lds_f32x2(mult);
+      sw = m.x;
+      bias_acc += m.y;
+    }
+#pragma unroll
+    for (int k = 0; k < kVPL; ++k) {
+      const int v = k * 32 + lane;
+      if (kVPL == 1 || v < nvec) {
+        if constexpr (kScaled) {
+          Row::fma(acc[k], row, v, sw);
+        } else {
+          Row::add(acc[k], row, v);
+        }
+      }
+    }
+    row += copy_bytes;
+    mult += 8;
+  }
+}
+
+template <typename Row, bool kScaled>
+struct AddOrFma {
+  template <int kVPL>
+  static __device__ __forceinline__ void run(Acc4 (&acc)[kVPL], float& bias_acc, uint32_t row,
+                                             uint32_t mult, int copy_bytes, int n, int nvec,
+                                             int lane) {
+    consume_rows<Row, kVPL, true>(acc, bias_acc, row, mult, copy_bytes, n, nvec, lane);
+  }
+};
+template <typename Row>
+struct AddOrFma<Row, false> {
+  template <int kVPL>
+  static __device__ __forceinline__ void run(Acc4 (&acc)[kVPL], float& bias_acc, uint32_t row,
+                                             uint32_t mult, int copy_bytes, int n, int nvec,
+                                             int lane) {
+    if (mult != 0) {
+      consume_rows<Row, kVPL, true>(acc, bias_acc, row, mult, copy_bytes, n, nvec, lane);
+    } else {
+      consume_rows<Row, kVPL, false>(acc, bias_acc, row, 0, copy_bytes, n, nvec, lane);
+    }
+  }
 };
 
 // Pools the bags [b0, b0 + nb) of table t (nb <= 31): lookups offsets[t*B+b0] .. offsets[t*B+b0+nb).
@@ -200,11 +345,12 @@ __device__ __forceinline__ bool stream_unit(const StreamBags& bags, const Stream
   const int64_t num_stages = (p_end - p_begin + rows_per_stage - 1) / rows_per_stage;
   const bool weighted = bags.per_sample_weights != nullptr;
   const bool mean = bags.pooling_mode == B200TBE_POOL_MEAN;
-  constexpr int kU = kVPL == 1 ? 4 : (kVPL == 2 ? 2 : 1);  // rows read before any is consumed
+  // rows need a per-row multiplier when they carry a header or the lookups carry weights
+  const bool scaled = Row::kHasHeader || weighted;
 
-  float acc[kVPL][4];
+  Acc4 acc[kVPL];
 #pragma unroll
-  for (int k = 0; k < kVPL; ++k) acc[k][0] = acc[k][1] = acc[k][2] = acc[k][3] = 0.f;
+  for (int k = 0; k < kVPL; ++k) acc[k].lo = acc[k].hi = make_float2(0.f, 0.f);
   float bias_acc = 0.f;
   int cur_bag = 0;
   int64_t cur_start = p_begin;
@@ -219,14 +365,11 @@ __device__ __forceinline__ bool stream_unit(const StreamBags& bags, const Stream
     for (int k = 0; k < kVPL; ++k) {
       const int v = k * 32 + lane;
       if (v < tab.nvec) {
-        float r[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          r[e] = (acc[k][e] + bias_acc) * scale;
-          acc[k][e] = 0.f;
-        }
+        const float r[4] = {(acc[k].lo.x + bias_acc) * scale, (acc[k].lo.y + bias_acc) * scale,
+                            (acc[k].hi.x + bias_acc) * scale, (acc[k].hi.y + bias_acc) * scale};
         store_pooled<OT, 4>(dst + 4 * v, r);
       }
+      acc[k].lo = acc[k].hi = make_float2(0.f, 0.f);
     }
     bias_acc = 0.f;
     ++cur_bag;
@@ -320,46 +463,39 @@ __device__ __forceinline__ bool stream_unit(const StreamBags& bags, const Stream
     const uint32_t vmask = ring.valid[slot];
     const int64_t pos0 = p_begin + stage * rows_per_stage;
     const int nr = p_end - pos0 < rows_per_stage ? static_cast<int>(p_end - pos0) : rows_per_stage;
+    const uint32_t rows_addr = smem_u32(ring.rows[slot]);
+    uint32_t mult_addr = 0;
+    if (scaled) {
+      // side table: lane i turns row i's header and weight into {multiplier, bias term}
+      float sw = weighted ? ring.weights[slot][lane] : 1.f, bw = 0.f;
+      if (Row::kHasHeader) {
+        const float2 sb = ((vmask >> lane) & 1u)
+                              ? half2_bits_to_float2(lds_u32(rows_addr + lane * tab.copy_bytes))
+                              : make_float2(0.f, 0.f);
+        bw = sb.y * sw;
+        sw *= sb.x;
+      }
+      ring.mult[slot][lane] = make_float2(sw, bw);
+      mult_addr = smem_u32(ring.mult[slot]);
+      __syncwarp();
+    }
+    const bool all_valid = vmask == (nr == 32 ? 0xffffffffu : ((1u << nr) - 1u));
     int r = 0;
     while (r < nr) {
       while (pos0 + r == cur_end) flush();
       const int64_t left_in_bag = cur_end - (pos0 + r);
       const int n = left_in_bag < nr - r ? static_cast<int>(left_in_bag) : nr - r;
-      for (int q = 0; q < n; q += kU) {
-        float4 x[kU][kVPL];
-        RowHeader h[kU];
-        float w[kU];
-#pragma unroll
-        for (int u = 0; u < kU; ++u) {
-          const int rr = r + q + u;
-          const bool live = q + u < n && ((vmask >> rr) & 1u);
-          w[u] = 0.f;
-          h[u] = {0.f, 0.f};
-          if (live) {
-            const char* row = ring.rows[slot] + rr * tab.copy_bytes;
-            w[u] = weighted ? ring.weights[slot][rr] : 1.f;
-            h[u] = Row::header(row);
-#pragma unroll
-            for (int k = 0; k < kVPL; ++k) {
-              const int v = k * 32 + lane;
-              x[u][k] = v < tab.nvec ? Row::load4(row, v) : make_float4(0.f, 0.f, 0.f, 0.f);
-            }
-          } else {
-#pragma unroll
-            for (int k = 0; k < kVPL; ++k) x[u][k] = make_float4(0.f, 0.f, 0.f, 0.f);
-          }
-        }
-#pragma unroll
-        for (int u = 0; u < kU; ++u) {
-          const float sw = h[u].scale * w[u];
-          bias_acc = fmaf(h[u].bias, w[u], bias_acc);
-#pragma unroll
-          for (int k = 0; k < kVPL; ++k) {
-            acc[k][0] = fmaf(x[u][k].x, sw, acc[k][0]);
-            acc[k][1] = fmaf(x[u][k].y, sw, acc[k][1]);
-            acc[k][2] = fmaf(x[u][k].z, sw, acc[k][2]);
-            acc[k][3] = fmaf(x[u][k].w, sw, acc[k][3]);
-          }
+      if (all_valid) {
+        AddOrFma<Row, Row::kHasHeader>::run(acc, bias_acc, rows_addr + r * tab.copy_bytes,
+                                            scaled ? mult_addr + r * 8 : 0, tab.copy_bytes, n,
+                                            tab.nvec, lane);
+      } else {
+        // some lookups of this stage were out of range: their rows were never copied
+        for (int i = 0; i < n; ++i) {
+          if ((vmask >> (r + i)) & 1u)
+            AddOrFma<Row, Row::kHasHeader>::run(acc, bias_acc, rows_addr + (r + i) * tab.copy_bytes,
+                                                scaled ? mult_addr + (r + i) * 8 : 0,
+                                                tab.copy_bytes, 1, tab.nvec, lane);
         }
       }
       r += n;
