@@ -210,6 +210,29 @@ B200TBE_API int b200tbe_radix_sort_pairs(void* keys_in, uint32_t* vals_in, void*
                                          b200tbe_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Gradient exchange of the table-wise-sharded configuration (the step a sharded caller runs between
+ * its dense part and b200tbe_backward; the pooled rows travel the other way inside b200tbe_forward,
+ * which can scatter into peer-mapped destination buffers). Source s is a peer's gradient matrix
+ * with rows src_stride_bytes apart; the row block [src_col_offset_bytes, +row_bytes) of its rows
+ * [0, rows_per_src) lands in rows [s*rows_per_src, (s+1)*rows_per_src) of dst. All byte counts and
+ * pointers must be multiples of 16. The kernel only reads the sources; making sure they are
+ * complete before, and not overwritten during, the call is the caller's job.
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* srcs[B200TBE_MAX_DESTS]; /* one per source rank, peer-mapped or local */
+  void* dst;
+  int64_t src_stride_bytes;
+  int64_t src_col_offset_bytes;
+  int64_t dst_stride_bytes;
+  int64_t rows_per_src;
+  int64_t row_bytes;
+  int32_t num_srcs;
+} b200tbe_exchange_pull_params;
+
+B200TBE_API int b200tbe_exchange_pull(const b200tbe_exchange_pull_params* p,
+                                      b200tbe_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Jagged tensors. values is [total_rows, inner_size]; dense is [outer_size, max_lengths[0], ...,
  * max_lengths[n-1], inner_size]; offsets[d] is the d-th level's offsets array (offsets[0] has
  * outer_size + 1 entries). Elements are moved as raw bytes, so any dtype of elem_bytes 1, 2, 4 or 8

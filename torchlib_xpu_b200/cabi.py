@@ -67,6 +67,14 @@ class BackwardParams(ctypes.Structure):
     ]
 
 
+class ExchangePullParams(ctypes.Structure):
+    _fields_ = [
+        ("srcs", _c_void_p * MAX_DESTS), ("dst", _c_void_p), ("src_stride_bytes", ctypes.c_int64),
+        ("src_col_offset_bytes", ctypes.c_int64), ("dst_stride_bytes", ctypes.c_int64),
+        ("rows_per_src", ctypes.c_int64), ("row_bytes", ctypes.c_int64), ("num_srcs", ctypes.c_int32),
+    ]
+
+
 class JaggedShape(ctypes.Structure):
     _fields_ = [
         ("offsets", _c_void_p * MAX_JAGGED_DIMS), ("max_lengths", ctypes.c_int64 * MAX_JAGGED_DIMS),
@@ -80,7 +88,7 @@ class JaggedShape(ctypes.Structure):
 EXPORTS = (
     "b200tbe_status_string", "b200tbe_abi_version", "b200tbe_forward", "b200tbe_nbit_forward",
     "b200tbe_backward_scratch_bytes", "b200tbe_backward", "b200tbe_radix_sort_scratch_bytes",
-    "b200tbe_radix_sort_pairs", "b200tbe_jagged_to_padded_dense", "b200tbe_dense_to_jagged",
+    "b200tbe_radix_sort_pairs", "b200tbe_exchange_pull", "b200tbe_jagged_to_padded_dense", "b200tbe_dense_to_jagged",
     "b200tbe_jagged_dense_elementwise_add",
 )
 
@@ -111,6 +119,7 @@ def lib() -> ctypes.CDLL:
         _lib.b200tbe_radix_sort_pairs.argtypes = [
             _c_void_p, _c_void_p, _c_void_p, _c_void_p, ctypes.c_int64, ctypes.c_int32,
             ctypes.c_int32, _c_void_p, ctypes.c_size_t, _c_void_p]
+        _lib.b200tbe_exchange_pull.argtypes = [ctypes.POINTER(ExchangePullParams), _c_void_p]
         _lib.b200tbe_forward.argtypes = [ctypes.POINTER(ForwardParams), _c_void_p]
         _lib.b200tbe_nbit_forward.argtypes = [ctypes.POINTER(NbitForwardParams), _c_void_p]
         _lib.b200tbe_backward.argtypes = [ctypes.POINTER(BackwardParams), _c_void_p]
@@ -250,6 +259,19 @@ def radix_sort_pairs(keys, vals, key_bits):
                                          keys.element_size(), key_bits, _p(scratch),
                                          scratch.numel(), _stream()), "b200tbe_radix_sort_pairs")
     return keys_out, vals_out
+
+
+def exchange_pull(src_ptrs, dst, src_stride_bytes, src_col_offset_bytes, rows_per_src, row_bytes):
+    """b200tbe_exchange_pull: src_ptrs are raw device addresses (peer-mapped buffers), dst a tensor
+    of [len(src_ptrs) * rows_per_src, row_bytes / element size]."""
+    p = ExchangePullParams()
+    for i, ptr in enumerate(src_ptrs):
+        p.srcs[i] = int(ptr)
+    p.dst = _p(dst)
+    p.src_stride_bytes, p.src_col_offset_bytes = src_stride_bytes, src_col_offset_bytes
+    p.dst_stride_bytes = dst.stride(0) * dst.element_size()
+    p.rows_per_src, p.row_bytes, p.num_srcs = rows_per_src, row_bytes, len(src_ptrs)
+    check(lib().b200tbe_exchange_pull(ctypes.byref(p), _stream()), "b200tbe_exchange_pull")
 
 
 def _jagged_shape(offsets_list, max_lengths, outer, inner, total_rows, elem_bytes, dtype_code):

@@ -1,0 +1,125 @@
+"""Table-wise sharding of TBE across the GPUs of one node: one process per GPU.
+
+Rank r owns T_local tables and looks them up for the WHOLE global batch of B bags; every rank ends
+up with the pooled rows of its own slice of the batch (B / G bags) for ALL tables:
+
+    pooled[r] : [B / G, G * D_local]     columns [s*D_local, (s+1)*D_local) come from rank s
+
+(with tables dealt round-robin, global table id = local_table * G + rank). The exchange is not a
+separate collective on the forward path: b200tbe_forward writes each pooled vector straight into the
+destination rank's receive buffer through its peer mapping (plain 16-byte stores over NVLink), and a
+stream-ordered barrier closes the step. On the way back each rank pulls its tables' column block of
+every peer's gradient matrix with b200tbe_exchange_pull, then runs the local fused backward.
+
+`layout_*` below are pure index arithmetic and are what the CPU (gloo) tests exercise;
+`reference_exchange` is the same data movement as an all_to_all_single, used as the baseline on
+GPUs (NCCL) and as the checker on CPU (gloo).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+
+def owner_of_table(global_table: int, world: int) -> int:
+    return global_table % world
+
+
+def local_tables(rank: int, world: int, total_tables: int) -> list[int]:
+    """Global ids of the tables rank holds, in its local order."""
+    return list(range(rank, total_tables, world))
+
+
+def layout_pooled_columns(rank_of_source: int, local_D: int) -> tuple[int, int]:
+    """Column range, in a receive buffer, of the pooled rows produced by one source rank."""
+    return rank_of_source * local_D, (rank_of_source + 1) * local_D
+
+
+def layout_batch_rows(rank: int, world: int, B: int) -> tuple[int, int]:
+    """Global bags whose pooled rows rank receives."""
+    if B % world != 0:
+        raise ValueError("global batch %d is not divisible by world size %d" % (B, world))
+    per = B // world
+    return rank * per, (rank + 1) * per
+
+
+def reference_exchange(pooled_local: torch.Tensor, group=None) -> torch.Tensor:
+    """[B, D_local] on every rank -> [B / G, G * D_local] on every rank, by all_to_all_single."""
+    world = dist.get_world_size(group)
+    B, local_D = pooled_local.shape
+    per = B // world
+    recv = torch.empty((world, per, local_D), dtype=pooled_local.dtype, device=pooled_local.device)
+    dist.all_to_all_single(recv, pooled_local.contiguous().view(world, per, local_D), group=group)
+    return recv.permute(1, 0, 2).reshape(per, world * local_D)
+
+
+def reference_gradient_exchange(grad_slice: torch.Tensor, group=None) -> torch.Tensor:
+    """[B / G, G * D_local] on every rank -> [B, D_local] on every rank (the transpose of the above)."""
+    world = dist.get_world_size(group)
+    per, total = grad_slice.shape
+    local_D = total // world
+    send = grad_slice.view(per, world, local_D).permute(1, 0, 2).contiguous()
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)
+    return recv.view(world * per, local_D)
+
+
+class PooledExchange:
+    """Peer-mapped receive / gradient buffers and the fused exchange for one rank (CUDA only)."""
+
+    def __init__(self, rank: int, world: int, B: int, local_D: int, dtype=torch.float16):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        if world > 16:
+            raise ValueError("at most 16 destinations")
+        self.rank, self.world, self.B, self.local_D = rank, world, B, local_D
+        self.per = layout_batch_rows(rank, world, B)[1] - layout_batch_rows(rank, world, B)[0]
+        self.dtype = dtype
+        dev = torch.device("cuda", torch.cuda.current_device())
+        # what this rank receives in the forward, and the gradient it hands back in the backward
+        self.recv = symm_mem.empty((self.per, world * local_D), dtype=dtype, device=dev)
+        self.grad_slice = symm_mem.empty((self.per, world * local_D), dtype=dtype, device=dev)
+        self._recv_hdl = symm_mem.rendezvous(self.recv, dist.group.WORLD)
+        self._grad_hdl = symm_mem.rendezvous(self.grad_slice, dist.group.WORLD)
+        self.recv_ptrs = [int(p) for p in self._recv_hdl.buffer_ptrs]
+        self.grad_ptrs = [int(p) for p in self._grad_hdl.buffer_ptrs]
+        self.grad_local = torch.empty((B, local_D), dtype=dtype, device=dev)
+        self._token = torch.zeros(1, device=dev)
+        gen = torch.Generator(device=dev).manual_seed(4242 + rank)
+        self.grad_slice.copy_(torch.randn((self.per, world * local_D), device=dev, generator=gen).to(dtype))
+        self.barrier()
+
+    def barrier(self):
+        """Stream-ordered barrier across ranks: everything enqueued before it on every rank has
+        finished before anything enqueued after it on any rank starts."""
+        dist.all_reduce(self._token)
+
+    def forward_lookup(self, step):
+        """Lookup of this rank's tables for the whole batch, pooled vectors written directly into
+        the owning ranks' receive buffers."""
+        from . import cabi
+
+        cabi.forward(step.weights, step.weights_offsets, step.D_offsets, step.total_D, step.D,
+                     step.indices, step.offsets, step.B, outputs=self.recv_ptrs,
+                     output_stride=self.world * self.local_D,
+                     output_col_offset=self.rank * self.local_D, rows_per_dest=self.per,
+                     output_dtype=self.dtype)
+        self.barrier()
+
+    def gather_gradients(self, step):
+        """Pulls this rank's column block of every peer's gradient matrix; returns [B, local_D]."""
+        from . import cabi
+
+        esz = self.grad_slice.element_size()
+        cabi.exchange_pull(self.grad_ptrs, self.grad_local, self.world * self.local_D * esz,
+                           self.rank * self.local_D * esz, self.per, self.local_D * esz)
+        self.barrier()
+        return self.grad_local
+
+    def launches_per_step(self) -> int:
+        return 1  # the pull kernel (the forward scatter is part of the lookup kernel)
+
+    def describe(self) -> str:
+        return ("pooled rows stored by the lookup kernel into peer receive buffers (NVLink P2P "
+                "stores); gradients pulled from peers by one copy kernel; NCCL all-reduce of one "
+                "element as the barrier after each")
