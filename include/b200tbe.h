@@ -209,6 +209,23 @@ B200TBE_API int b200tbe_radix_sort_pairs(void* keys_in, uint32_t* vals_in, void*
                                          int32_t key_bits, void* scratch, size_t scratch_bytes,
                                          b200tbe_stream_t stream);
 
+/* The same sort for callers that cannot allocate device memory when they call it -- a plain C or
+ * C++ host with no tensor allocator to borrow scratch from, a server that has already given all of
+ * HBM to its tables, a loop that cannot take the device-wide synchronisation of cudaMalloc. The
+ * scratch is a fixed array inside the library (about 513 KiB on every GPU that loads it, held
+ * until the process exits), so n is limited to b200tbe_radix_sort_pairs_static_max() = 2^20 pairs;
+ * larger n returns B200TBE_ERR_TOO_LARGE. The entry point calls no cudaMalloc, cudaFree or other
+ * allocating routine. Its first call on a device looks up the array's device address (once per
+ * device, with that device current); make that first call before any stream capture begins.
+ * All calls on a device share the array: two calls whose kernels can overlap on the GPU (different
+ * streams without an ordering between them) race on it and must be serialised by the caller.
+ * Nothing in the array needs clearing between calls. This entry point has no counterpart in
+ * intel/torchlib-xpu or in fbgemm_gpu. Other arguments as b200tbe_radix_sort_pairs. */
+B200TBE_API int64_t b200tbe_radix_sort_pairs_static_max(void);
+B200TBE_API int b200tbe_radix_sort_pairs_static(void* keys_in, uint32_t* vals_in, void* keys_out,
+                                                uint32_t* vals_out, int64_t n, int32_t key_bytes,
+                                                int32_t key_bits, b200tbe_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Gradient exchange of the table-wise-sharded configuration (the step a sharded caller runs between
  * its dense part and b200tbe_backward; the pooled rows travel the other way inside b200tbe_forward,

@@ -88,7 +88,8 @@ class JaggedShape(ctypes.Structure):
 EXPORTS = (
     "b200tbe_status_string", "b200tbe_abi_version", "b200tbe_forward", "b200tbe_nbit_forward",
     "b200tbe_backward_scratch_bytes", "b200tbe_backward", "b200tbe_radix_sort_scratch_bytes",
-    "b200tbe_radix_sort_pairs", "b200tbe_exchange_pull", "b200tbe_jagged_to_padded_dense", "b200tbe_dense_to_jagged",
+    "b200tbe_radix_sort_pairs", "b200tbe_radix_sort_pairs_static_max",
+    "b200tbe_radix_sort_pairs_static", "b200tbe_exchange_pull", "b200tbe_jagged_to_padded_dense", "b200tbe_dense_to_jagged",
     "b200tbe_jagged_dense_elementwise_add",
 )
 
@@ -119,6 +120,11 @@ def lib() -> ctypes.CDLL:
         _lib.b200tbe_radix_sort_pairs.argtypes = [
             _c_void_p, _c_void_p, _c_void_p, _c_void_p, ctypes.c_int64, ctypes.c_int32,
             ctypes.c_int32, _c_void_p, ctypes.c_size_t, _c_void_p]
+        _lib.b200tbe_radix_sort_pairs_static_max.restype = ctypes.c_int64
+        _lib.b200tbe_radix_sort_pairs_static_max.argtypes = []
+        _lib.b200tbe_radix_sort_pairs_static.argtypes = [
+            _c_void_p, _c_void_p, _c_void_p, _c_void_p, ctypes.c_int64, ctypes.c_int32,
+            ctypes.c_int32, _c_void_p]
         _lib.b200tbe_exchange_pull.argtypes = [ctypes.POINTER(ExchangePullParams), _c_void_p]
         _lib.b200tbe_forward.argtypes = [ctypes.POINTER(ForwardParams), _c_void_p]
         _lib.b200tbe_nbit_forward.argtypes = [ctypes.POINTER(NbitForwardParams), _c_void_p]

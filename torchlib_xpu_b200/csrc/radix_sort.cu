@@ -236,3 +236,62 @@ extern "C" int b200tbe_radix_sort_pairs(void* keys_in, uint32_t* vals_in, void* 
   }
   return B200TBE_OK;
 }
+
+// ------------------------------------------------------------------------------------------------
+// Sort entry point that allocates nothing.
+//
+// Some callers of this library cannot obtain device memory at call time: a C or C++ host that links
+// libb200tbe.so directly and has no tensor allocator to borrow scratch from; a serving process that
+// reserves all of HBM for embedding tables at start-up, so a later cudaMalloc may fail; and
+// latency-critical loops that cannot afford the device-wide synchronisation cudaMalloc and cudaFree
+// imply. For them the sort's scratch (per-tile digit counts and the scan's tile sums) lives in a
+// fixed array inside the library. Every GPU that loads the library holds the array until the
+// process exits, which is why the capacity is modest.
+// ------------------------------------------------------------------------------------------------
+namespace b200tbe {
+namespace {
+
+constexpr int64_t kStaticSortMaxPairs = int64_t{1} << 20;
+// counts for the narrower (8-byte-key) tile + scan tile sums + slack, as radix_sort_scratch_bytes()
+// computes for kStaticSortMaxPairs: 512 tiles x 256 digits x 4 B = 512 KiB, plus under 1 KiB.
+constexpr size_t kStaticSortScratchBytes = (size_t{512} * 256 * 4) + 1024;
+
+static __device__ __align__(256) unsigned char g_static_sort_scratch[kStaticSortScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_static_sort_ptr[kMaxDevices] = {};
+
+// The array's name is only a host-side handle; the device address has to be asked for, once per
+// device, with that device current.
+int static_sort_scratch(void** out) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return B200TBE_ERR_LAUNCH;
+  void* p = __atomic_load_n(&g_static_sort_ptr[dev], __ATOMIC_ACQUIRE);
+  if (p == nullptr) {
+    if (cudaGetSymbolAddress(&p, g_static_sort_scratch) != cudaSuccess || p == nullptr)
+      return B200TBE_ERR_LAUNCH;
+    __atomic_store_n(&g_static_sort_ptr[dev], p, __ATOMIC_RELEASE);
+  }
+  *out = p;
+  return B200TBE_OK;
+}
+
+}  // namespace
+}  // namespace b200tbe
+
+extern "C" int64_t b200tbe_radix_sort_pairs_static_max(void) { return kStaticSortMaxPairs; }
+
+extern "C" int b200tbe_radix_sort_pairs_static(void* keys_in, uint32_t* vals_in, void* keys_out,
+                                               uint32_t* vals_out, int64_t n, int32_t key_bytes,
+                                               int32_t key_bits, b200tbe_stream_t stream_) {
+  if (n < 0) return B200TBE_ERR_BAD_ARG;
+  if (n > kStaticSortMaxPairs) return B200TBE_ERR_TOO_LARGE;
+  static_assert(kStaticSortScratchBytes >= 256, "scratch too small");
+  if (radix_sort_scratch_bytes(n) > kStaticSortScratchBytes) return B200TBE_ERR_TOO_LARGE;
+  void* scratch = nullptr;
+  const int st = static_sort_scratch(&scratch);
+  if (st != B200TBE_OK) return st;
+  // Nothing in the scratch has to start at zero: every pass rewrites all the counts it reads.
+  return b200tbe_radix_sort_pairs(keys_in, vals_in, keys_out, vals_out, n, key_bytes, key_bits,
+                                  scratch, kStaticSortScratchBytes, stream_);
+}
