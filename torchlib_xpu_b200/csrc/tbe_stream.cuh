@@ -10,7 +10,7 @@
 // then consumes stages in order: one row per instruction, lane v taking elements [4v, 4v+4) of the
 // row from shared memory, accumulating in fp32 registers, and writing a bag's pooled vector when
 // the stream of lookups crosses the bag's end. Two stages are in flight while a third is being
-// consumed; 8 warps x 2 stages x 8 KB = 128 KB in flight per SM.
+// consumed; 16 warps x 2 stages x 4 KB = 128 KB in flight per SM.
 //
 // Work is cut into units of a few consecutive bags of one table (so a unit's lookups are one
 // contiguous range of the index array and its table parameters are warp-uniform); a persistent
@@ -23,13 +23,26 @@
 
 #include "tbe_pool.cuh"
 
+// Two ways to fill a ring stage. Default: cp.async (16 bytes per lane, 32 consecutive chunks per
+// instruction, through L1 so that the hottest rows hit there). -DB200TBE_STREAM_BULK selects one
+// cp.async.bulk per row instead; measured on B200 it is slower for rows of a few hundred bytes,
+// because a bulk copy issued by 32 lanes executes as 32 separate instructions (one TMA instruction
+// per row, about 20 warp instructions of overhead each).
+#ifndef B200TBE_STREAM_BULK
+#define B200TBE_STREAM_LDGSTS 1
+#endif
+
 namespace b200tbe {
 
-constexpr int kStreamWarps = 8;
+constexpr int kStreamWarps = 16;
 constexpr int kStreamThreads = kStreamWarps * 32;
 constexpr int kStages = 3;
-constexpr int kStageBytes = 8192;
-constexpr int kWaitSpins = 1 << 22;  // bounded mbarrier wait (each try blocks for a short while)
+constexpr int kStageBytes = 4096;
+// Bounded mbarrier wait: each try suspends the thread in hardware for up to kWaitHintNs (it wakes
+// as soon as the phase completes), so a waiting warp issues almost no instructions; after
+// kWaitSpins tries (about two seconds) the wait gives up.
+constexpr int kWaitSpins = 1 << 17;
+constexpr uint32_t kWaitHintNs = 16384;
 
 struct WarpRing {
   alignas(128) char rows[kStages][kStageBytes];
@@ -59,11 +72,11 @@ __device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, uint32_t 
   asm volatile(
       "{\n"
       ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
       "selp.u32 %0, 1, 0, p;\n"
       "}\n"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(kWaitHintNs)
       : "memory");
   return ok != 0;
 }
@@ -181,9 +194,17 @@ struct FloatRow<__half> {
   static constexpr bool kHasHeader = false;
   static constexpr int kHeaderBytes = 0;
   static __device__ __forceinline__ void add(Acc4& a, uint32_t row, int v) {
+    // fp32 accumulator += fp16 element in one instruction (mixed-precision add of sm_100)
     const uint2 x = lds_u64(row + (v << 3));
-    a.lo = __fadd2_rn(a.lo, half2_bits_to_float2(x.x));
-    a.hi = __fadd2_rn(a.hi, half2_bits_to_float2(x.y));
+    asm("{.reg .f16 l0, h0, l1, h1;\n"
+        "mov.b32 {l0, h0}, %4;\n"
+        "mov.b32 {l1, h1}, %5;\n"
+        "add.rn.f32.f16 %0, l0, %0;\n"
+        "add.rn.f32.f16 %1, h0, %1;\n"
+        "add.rn.f32.f16 %2, l1, %2;\n"
+        "add.rn.f32.f16 %3, h1, %3;}\n"
+        : "+f"(a.lo.x), "+f"(a.lo.y), "+f"(a.hi.x), "+f"(a.hi.y)
+        : "r"(x.x), "r"(x.y));
   }
   static __device__ __forceinline__ void fma(Acc4& a, uint32_t row, int v, float sw) {
     const uint2 x = lds_u64(row + (v << 3));
@@ -252,42 +273,17 @@ struct StreamOut {
   int64_t rows_per_dest;
 };
 
-// n consecutive rows, all valid, no bag boundary inside. kScaled: every row has a {multiplier, bias
-// term} pair in the stage's side table (quantised rows and/or per-sample weights).
-template <typename Row, int kVPL, bool kScaled>
-__device__ __forceinline__ void consume_rows(Acc4 (&acc)[kVPL], float& bias_acc, uint32_t row,
-                                             uint32_t mult, int copy_bytes, int n, int nvec,
-                                             int lane) {
-  constexpr int kU = kVPL == 1 ? 4 : (kVPL == 2 ? 2 : 1);
-  int i = 0;
-  for (; i + kU <= n; i += kU) {
+// kN consecutive rows starting at shared address `row`, all valid, all of one bag, fully unrolled:
+// the loads of all kN rows are independent of each other. kScaled: every row has a {multiplier,
+// bias term} pair in the stage's side table (quantised rows and/or per-sample weights).
+template <typename Row, int kVPL, bool kScaled, int kN>
+__device__ __forceinline__ void consume_fixed(Acc4 (&acc)[kVPL], float& bias_acc, uint32_t row,
+                                              uint32_t mult, int copy_bytes, int nvec, int lane) {
 #pragma unroll
-    for (int u = 0; u < kU; ++u) {
-      float sw = 1.f;
-      if (kScaled) {
-        const float2 m = lds_f32x2(mult + 8 * u);
-        sw = m.x;
-        bias_acc += m.y;
-      }
-#pragma unroll
-      for (int k = 0; k < kVPL; ++k) {
-        const int v = k * 32 + lane;
-        if (kVPL == 1 || v < nvec) {
-          if constexpr (kScaled) {
-            Row::fma(acc[k], row + u * copy_bytes, v, sw);
-          } else {
-            Row::add(acc[k], row + u * copy_bytes, v);
-          }
-        }
-      }
-    }
-    row += kU * copy_bytes;
-    mult += kU * 8;
-  }
-  for (; i < n; ++i) {
+  for (int u = 0; u < kN; ++u) {
     float sw = 1.f;
     if (kScaled) {
-      const float2 m = lds_f32x2(mult);
+      const float2 m = lds_f32x2(mult + 8 * u);
       sw = m.x;
       bias_acc += m.y;
     }
@@ -296,122 +292,181 @@ __device__ __forceinline__ void consume_rows(Acc4 (&acc)[kVPL], float& bias_acc,
       const int v = k * 32 + lane;
       if (kVPL == 1 || v < nvec) {
         if constexpr (kScaled) {
-          Row::fma(acc[k], row, v, sw);
+          Row::fma(acc[k], row + u * copy_bytes, v, sw);
         } else {
-          Row::add(acc[k], row, v);
+          Row::add(acc[k], row + u * copy_bytes, v);
         }
       }
     }
-    row += copy_bytes;
-    mult += 8;
   }
 }
 
-template <typename Row, bool kScaled>
-struct AddOrFma {
-  template <int kVPL>
-  static __device__ __forceinline__ void run(Acc4 (&acc)[kVPL], float& bias_acc, uint32_t row,
-                                             uint32_t mult, int copy_bytes, int n, int nvec,
-                                             int lane) {
-    consume_rows<Row, kVPL, true>(acc, bias_acc, row, mult, copy_bytes, n, nvec, lane);
-  }
-};
-template <typename Row>
-struct AddOrFma<Row, false> {
-  template <int kVPL>
-  static __device__ __forceinline__ void run(Acc4 (&acc)[kVPL], float& bias_acc, uint32_t row,
-                                             uint32_t mult, int copy_bytes, int n, int nvec,
-                                             int lane) {
+// Rows with a header are always scaled; float rows only when the lookups carry weights (mult != 0).
+template <typename Row, int kVPL, int kN>
+__device__ __forceinline__ void consume(Acc4 (&acc)[kVPL], float& bias_acc, uint32_t row,
+                                        uint32_t mult, int copy_bytes, int nvec, int lane) {
+  if constexpr (Row::kHasHeader) {
+    consume_fixed<Row, kVPL, true, kN>(acc, bias_acc, row, mult, copy_bytes, nvec, lane);
+  } else {
     if (mult != 0) {
-      consume_rows<Row, kVPL, true>(acc, bias_acc, row, mult, copy_bytes, n, nvec, lane);
+      consume_fixed<Row, kVPL, true, kN>(acc, bias_acc, row, mult, copy_bytes, nvec, lane);
     } else {
-      consume_rows<Row, kVPL, false>(acc, bias_acc, row, 0, copy_bytes, n, nvec, lane);
+      consume_fixed<Row, kVPL, false, kN>(acc, bias_acc, row, 0, copy_bytes, nvec, lane);
     }
   }
-};
+}
 
 // Pools the bags [b0, b0 + nb) of table t (nb <= 31): lookups offsets[t*B+b0] .. offsets[t*B+b0+nb).
 // `phases` holds one parity bit per ring stage and lives across units. Returns false if a wait
-// timed out (the caller must stop using the ring).
+// timed out (the caller must stop using the ring). Positions inside the unit are 32-bit offsets
+// from the unit's first lookup (a unit is at most 31 bags long).
 template <typename Row, typename OT, typename IndexT, int kVPL>
 __device__ __forceinline__ bool stream_unit(const StreamBags& bags, const StreamTable& tab,
                                             const StreamOut<OT>& out, int64_t bag0, int b0, int nb,
                                             WarpRing& ring, uint32_t& phases, int lane) {
-  // lane j holds the start of bag j of the unit (j = nb: the unit's end)
-  const int64_t my_off = lane <= nb ? load_index<IndexT>(bags.offsets, bag0 + lane) : 0;
-  const int64_t p_begin = __shfl_sync(kFullMask, my_off, 0);
-  const int64_t p_end = __shfl_sync(kFullMask, my_off, nb);
+  // lane j holds the start of bag j of the unit (j = nb: the unit's end), relative to the unit
+  const int64_t my_off64 = lane <= nb ? load_index<IndexT>(bags.offsets, bag0 + lane) : 0;
+  const int64_t p_begin = __shfl_sync(kFullMask, my_off64, 0);
+  const int my_off = lane <= nb ? static_cast<int>(my_off64 - p_begin) : 0x7fffffff;
+  const int total = __shfl_sync(kFullMask, my_off, nb);
   const int rows_per_stage = min(32, kStageBytes / tab.copy_bytes);
-  const int64_t num_stages = (p_end - p_begin + rows_per_stage - 1) / rows_per_stage;
+  const int num_stages = (total + rows_per_stage - 1) / rows_per_stage;
   const bool weighted = bags.per_sample_weights != nullptr;
   const bool mean = bags.pooling_mode == B200TBE_POOL_MEAN;
   // rows need a per-row multiplier when they carry a header or the lookups carry weights
   const bool scaled = Row::kHasHeader || weighted;
+  const IndexT* idx_base = reinterpret_cast<const IndexT*>(bags.indices) + p_begin;
+  const float* psw_base = weighted ? bags.per_sample_weights + p_begin : nullptr;
+
+  // destination of the unit's first bag; bags of a unit are consecutive rows of one destination
+  // unless the unit straddles a destination boundary
+  const int rpd = static_cast<int>(out.rows_per_dest);
+  const int dest0 = b0 / rpd;
+  const bool one_dest = (b0 + nb - 1) / rpd == dest0;
+  OT* dst_next = out.outputs[dest0] + static_cast<int64_t>(b0 - dest0 * rpd) * out.output_stride +
+                 out.col + 4 * lane;
 
   Acc4 acc[kVPL];
 #pragma unroll
   for (int k = 0; k < kVPL; ++k) acc[k].lo = acc[k].hi = make_float2(0.f, 0.f);
   float bias_acc = 0.f;
   int cur_bag = 0;
-  int64_t cur_start = p_begin;
-  int64_t cur_end = __shfl_sync(kFullMask, my_off, 1);
+  int cur_start = 0;
+  int cur_end = __shfl_sync(kFullMask, my_off, 1);
 
   auto flush = [&]() {
     const float scale = (mean && cur_end > cur_start) ? 1.f / static_cast<float>(cur_end - cur_start) : 1.f;
-    const int b = b0 + cur_bag;
-    const int dest = static_cast<int>(b / out.rows_per_dest);
-    OT* dst = out.outputs[dest] + (b - dest * out.rows_per_dest) * out.output_stride + out.col;
+    OT* dst = dst_next;
+    if (!one_dest) {
+      const int b = b0 + cur_bag;
+      const int dest = b / rpd;
+      dst = out.outputs[dest] + static_cast<int64_t>(b - dest * rpd) * out.output_stride + out.col +
+            4 * lane;
+    }
 #pragma unroll
     for (int k = 0; k < kVPL; ++k) {
-      const int v = k * 32 + lane;
-      if (v < tab.nvec) {
+      if (k * 32 + lane < tab.nvec) {
         const float r[4] = {(acc[k].lo.x + bias_acc) * scale, (acc[k].lo.y + bias_acc) * scale,
                             (acc[k].hi.x + bias_acc) * scale, (acc[k].hi.y + bias_acc) * scale};
-        store_pooled<OT, 4>(dst + 4 * v, r);
+        store_pooled<OT, 4>(dst + 128 * k, r);
       }
       acc[k].lo = acc[k].hi = make_float2(0.f, 0.f);
     }
     bias_acc = 0.f;
+    dst_next += out.output_stride;
     ++cur_bag;
     cur_start = cur_end;
     cur_end = __shfl_sync(kFullMask, my_off, (cur_bag + 1) & 31);
   };
 
-  // index of the lookup this lane will issue next, fetched one stage ahead
-  int64_t next_idx = 0;
-  auto prefetch_index = [&](int64_t stage) {
-    const int64_t pos = p_begin + stage * rows_per_stage + lane;
-    next_idx = (stage < num_stages && lane < rows_per_stage && pos < p_end)
-                   ? load_index<IndexT>(bags.indices, pos)
-                   : -1;
+  // indices of the lookups this lane will issue in the next kIdxAhead stages: the index loads run
+  // that many stages ahead of the row copies, which run kStages - 1 stages ahead of consumption
+  constexpr int kIdxAhead = 3;
+  int64_t idx_q[kIdxAhead];
+#ifdef B200TBE_STREAM_LDGSTS
+  const int chunks = tab.copy_bytes >> 4;                       // 16-byte chunks per row
+  const int copy_iters = (rows_per_stage * chunks + 31) >> 5;    // warp instructions per stage
+  const int chunk_shift = (chunks & (chunks - 1)) == 0 && chunks <= 32 ? __ffs(chunks) - 1 : -1;
+  const int lane_row0 = lane / chunks, lane_chunk0 = lane - lane_row0 * chunks;
+  const int row_step = 32 / chunks, chunk_step = 32 - row_step * chunks;
+#endif
+  int issue_pos = lane;   // position (relative) this lane issues in the next stage to be issued
+  int issue_slot = 0;
+  auto load_idx = [&](int pos) -> int64_t {
+    return (lane < rows_per_stage && pos < total) ? static_cast<int64_t>(__ldg(idx_base + pos)) : -1;
   };
-  auto issue = [&](int64_t stage) {
-    const int slot = static_cast<int>(stage % kStages);
-    const int64_t pos = p_begin + stage * rows_per_stage + lane;
-    const bool in_stage = lane < rows_per_stage && pos < p_end;
-    int64_t idx = next_idx;
-    prefetch_index(stage + 1);
+  auto issue = [&]() {
+    const int slot = issue_slot;
+    const int pos = issue_pos;
+    const bool in_stage = lane < rows_per_stage && pos < total;
+    const int64_t idx = idx_q[0];
+#pragma unroll
+    for (int q = 0; q + 1 < kIdxAhead; ++q) idx_q[q] = idx_q[q + 1];
+    idx_q[kIdxAhead - 1] = load_idx(pos + kIdxAhead * rows_per_stage);
+    issue_pos += rows_per_stage;
+    issue_slot = issue_slot + 1 == kStages ? 0 : issue_slot + 1;
     bool ok = in_stage;
     if (in_stage && tab.num_rows >= 0 && (idx < 0 || idx >= tab.num_rows)) {
       atomicOr(bags.status, B200TBE_DEV_INDEX_OUT_OF_RANGE);
       ok = false;
     }
     const uint32_t vmask = __ballot_sync(kFullMask, ok);
-    if (weighted) ring.weights[slot][lane] = in_stage ? __ldg(bags.per_sample_weights + pos) : 0.f;
+    if (weighted) ring.weights[slot][lane] = in_stage ? __ldg(psw_base + pos) : 0.f;
 #ifdef B200TBE_STREAM_LDGSTS
     if (lane == 0) ring.valid[slot] = vmask;
-    const int chunks = tab.copy_bytes >> 4;
-    const int total = rows_per_stage * chunks;
-    for (int i0 = 0; i0 < total; i0 += 32) {
-      const int i = i0 + lane;
-      const int row = i / chunks;
-      const int chunk = i - row * chunks;
-      const int64_t ridx = __shfl_sync(kFullMask, idx, row & 31);
-      if (i < total && ((vmask >> row) & 1u)) {
-        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(smem_u32(
-                         ring.rows[slot] + row * tab.copy_bytes + (chunk << 4))),
-                     "l"(tab.base + ridx * tab.stride + (chunk << 4))
-                     : "memory");
+    // lane i knows where row i of the stage lives (as a 16-byte chunk number inside the table);
+    // the copy itself runs over the stage buffer in 16-byte chunks, 32 consecutive chunks per
+    // instruction (coalesced on both sides)
+    const int64_t byte_off = idx * tab.stride;
+    const uint32_t my_chunk = ok ? static_cast<uint32_t>(byte_off >> 4) : 0xffffffffu;
+    const bool wide = __any_sync(kFullMask, ok && (byte_off >> 36) != 0);  // table beyond 64 GB
+    uint32_t dst = smem_u32(ring.rows[slot]) + (lane << 4);
+    if (wide) {
+      const char* my_src = ok ? tab.base + byte_off : nullptr;
+      int row = lane_row0, chunk = lane_chunk0;
+      for (int it = 0; it < copy_iters; ++it) {
+        const char* src = reinterpret_cast<const char*>(
+            __shfl_sync(kFullMask, reinterpret_cast<unsigned long long>(my_src), row & 31));
+        if (row < rows_per_stage && src != nullptr)
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src + (chunk << 4))
+                       : "memory");
+        row += row_step;
+        chunk += chunk_step;
+        if (chunk >= chunks) {
+          chunk -= chunks;
+          ++row;
+        }
+        dst += 512;
+      }
+    } else if (chunk_shift >= 0) {
+      // chunks per row is a power of two: a lane keeps its chunk and moves rows_per_it rows a step
+      const int rows_per_it = 32 >> chunk_shift;
+      const char* lane_base = tab.base + ((lane & ((1 << chunk_shift) - 1)) << 4);
+      int row = lane >> chunk_shift;
+      for (int it = 0; it < copy_iters; ++it) {
+        const uint32_t c = __shfl_sync(kFullMask, my_chunk, row);
+        if (c != 0xffffffffu)
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst),
+                       "l"(lane_base + (static_cast<uint64_t>(c) << 4))
+                       : "memory");
+        row += rows_per_it;
+        dst += 512;
+      }
+    } else {
+      int row = lane_row0, chunk = lane_chunk0;
+      for (int it = 0; it < copy_iters; ++it) {
+        const uint32_t c = __shfl_sync(kFullMask, my_chunk, row & 31);
+        if (row < rows_per_stage && c != 0xffffffffu)
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst),
+                       "l"(tab.base + ((static_cast<uint64_t>(c) + chunk) << 4))
+                       : "memory");
+        row += row_step;
+        chunk += chunk_step;
+        if (chunk >= chunks) {
+          chunk -= chunks;
+          ++row;
+        }
+        dst += 512;
       }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
@@ -426,10 +481,12 @@ __device__ __forceinline__ bool stream_unit(const StreamBags& bags, const Stream
 #endif
   };
 
-  prefetch_index(0);
-  for (int s = 0; s < kStages - 1; ++s) {
-    if (s < num_stages) {
-      issue(s);
+#pragma unroll
+  for (int q = 0; q < kIdxAhead; ++q) idx_q[q] = load_idx(lane + q * rows_per_stage);
+  int issued = 0;
+  for (; issued < kStages - 1; ++issued) {
+    if (issued < num_stages) {
+      issue();
     } else {
 #ifdef B200TBE_STREAM_LDGSTS
       asm volatile("cp.async.commit_group;" ::: "memory");
@@ -438,18 +495,19 @@ __device__ __forceinline__ bool stream_unit(const StreamBags& bags, const Stream
   }
   __syncwarp();
 
-  for (int64_t stage = 0; stage < num_stages; ++stage) {
+  int slot = 0;
+  int pos0 = 0;
+  for (int stage = 0; stage < num_stages; ++stage) {
     if (stage + kStages - 1 < num_stages) {
       // the slot being refilled was read by ordinary loads in the previous iteration
       fence_proxy_async_smem();
-      issue(stage + kStages - 1);
+      issue();
     } else {
 #ifdef B200TBE_STREAM_LDGSTS
       asm volatile("cp.async.commit_group;" ::: "memory");
 #endif
     }
     __syncwarp();
-    const int slot = static_cast<int>(stage % kStages);
 #ifdef B200TBE_STREAM_LDGSTS
     asm volatile("cp.async.wait_group %0;" ::"n"(kStages - 1) : "memory");
     __syncwarp();
@@ -461,8 +519,7 @@ __device__ __forceinline__ bool stream_unit(const StreamBags& bags, const Stream
     phases ^= 1u << slot;
 #endif
     const uint32_t vmask = ring.valid[slot];
-    const int64_t pos0 = p_begin + stage * rows_per_stage;
-    const int nr = p_end - pos0 < rows_per_stage ? static_cast<int>(p_end - pos0) : rows_per_stage;
+    const int nr = total - pos0 < rows_per_stage ? total - pos0 : rows_per_stage;
     const uint32_t rows_addr = smem_u32(ring.rows[slot]);
     uint32_t mult_addr = 0;
     if (scaled) {
@@ -480,27 +537,33 @@ __device__ __forceinline__ bool stream_unit(const StreamBags& bags, const Stream
       __syncwarp();
     }
     const bool all_valid = vmask == (nr == 32 ? 0xffffffffu : ((1u << nr) - 1u));
+    // groups of kG rows take the unrolled path when no bag ends inside the group; a group that
+    // holds a bag boundary (or an invalid row) goes row by row
+    constexpr int kG = kVPL == 1 ? 4 : (kVPL == 2 ? 2 : 1);
     int r = 0;
+    uint32_t row_addr = rows_addr;
+    uint32_t m_addr = mult_addr;
+    const int m_step = scaled ? 8 : 0;
     while (r < nr) {
-      while (pos0 + r == cur_end) flush();
-      const int64_t left_in_bag = cur_end - (pos0 + r);
-      const int n = left_in_bag < nr - r ? static_cast<int>(left_in_bag) : nr - r;
-      if (all_valid) {
-        AddOrFma<Row, Row::kHasHeader>::run(acc, bias_acc, rows_addr + r * tab.copy_bytes,
-                                            scaled ? mult_addr + r * 8 : 0, tab.copy_bytes, n,
-                                            tab.nvec, lane);
+      const int left_in_bag = cur_end - (pos0 + r);
+      if (all_valid && left_in_bag >= kG && nr - r >= kG) {
+        consume<Row, kVPL, kG>(acc, bias_acc, row_addr, m_addr, tab.copy_bytes, tab.nvec, lane);
+        r += kG;
+        row_addr += kG * tab.copy_bytes;
+        m_addr += kG * m_step;
       } else {
-        // some lookups of this stage were out of range: their rows were never copied
-        for (int i = 0; i < n; ++i) {
-          if ((vmask >> (r + i)) & 1u)
-            AddOrFma<Row, Row::kHasHeader>::run(acc, bias_acc, rows_addr + (r + i) * tab.copy_bytes,
-                                                scaled ? mult_addr + (r + i) * 8 : 0,
-                                                tab.copy_bytes, 1, tab.nvec, lane);
-        }
+        while (pos0 + r == cur_end) flush();
+        // a lookup that was out of range never had its row copied
+        if ((vmask >> r) & 1u)
+          consume<Row, kVPL, 1>(acc, bias_acc, row_addr, m_addr, tab.copy_bytes, tab.nvec, lane);
+        ++r;
+        row_addr += tab.copy_bytes;
+        m_addr += m_step;
       }
-      r += n;
     }
     __syncwarp();
+    pos0 += rows_per_stage;
+    slot = slot + 1 == kStages ? 0 : slot + 1;
   }
   while (cur_bag < nb) flush();
   return true;
