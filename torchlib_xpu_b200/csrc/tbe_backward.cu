@@ -14,7 +14,7 @@
 //               chunk order and applies the update. Summation order is fixed by the data alone.
 #include "radix_sort.cuh"
 #include "scan.cuh"
-#include "tbe_pool.cuh"
+#include "tbe_stream.cuh"
 
 namespace b200tbe {
 namespace {
@@ -348,6 +348,304 @@ __global__ void __launch_bounds__(kBwdThreads) reduce_runs_kernel(BwdDev p) {
   }
 }
 
+// ---- streaming reduction of runs -------------------------------------------------------------
+// The per-run reduction on the shared-memory ring engine of tbe_stream.cuh: a warp takes up to 31
+// consecutive runs, streams the gradient slices of all their lookups through its ring (cp.async,
+// two stages in flight), adds them up run by run, and applies the optimizer when the stream crosses
+// a run's end. Nothing in the steady state waits on a dependent global load: run starts, keys and
+// optimizer state are fetched once per group of runs, the weight rows are prefetched into L2 at
+// that point and loaded when their run begins, gradient rows arrive through the ring.
+
+// Applies the optimizer to one row. Lane v holds elements [4v, 4v+4) of vector k*32+v in acc[k].
+template <typename WT, int kVPL>
+__device__ __forceinline__ void apply_update4(const BwdDev& p, Acc4 (&acc)[kVPL], WT* w_row,
+                                              float* m_ptr, int D, int nvec, int lane) {
+  float mult = p.learning_rate;
+  if (p.optimizer == B200TBE_OPT_ROWWISE_ADAGRAD) {
+    float sq = 0.f;
+#pragma unroll
+    for (int k = 0; k < kVPL; ++k) {
+      if (k * 32 + lane < nvec) {
+        sq = fmaf(acc[k].lo.x, acc[k].lo.x, sq);
+        sq = fmaf(acc[k].lo.y, acc[k].lo.y, sq);
+        sq = fmaf(acc[k].hi.x, acc[k].hi.x, sq);
+        sq = fmaf(acc[k].hi.y, acc[k].hi.y, sq);
+      }
+    }
+    sq = warp_sum(sq);
+    float m_new = 0.f;
+    if (lane == 0) {
+      m_new = *m_ptr + sq / static_cast<float>(D);
+      *m_ptr = m_new;
+    }
+    m_new = __shfl_sync(kFullMask, m_new, 0);
+    mult = p.learning_rate / (sqrtf(m_new) + p.eps);
+  }
+#pragma unroll
+  for (int k = 0; k < kVPL; ++k) {
+    const int v = k * 32 + lane;
+    if (v < nvec) {
+      const float g[4] = {acc[k].lo.x, acc[k].lo.y, acc[k].hi.x, acc[k].hi.y};
+      update_elems4<WT>(w_row + 4 * v, g, mult);
+    }
+  }
+}
+
+struct RunGroup {
+  int t;                 // table of every run in the group
+  int D;
+  int nvec;              // D / 4
+  int copy_bytes;        // bytes of a gradient slice
+  const char* grad_col;  // grad_output + column of table t, in bytes
+  int64_t hash0;         // hash_size_cumsum[t]
+  int64_t bag0;          // t * B
+};
+
+// Reduces and updates the runs [first_run, first_run + nb) (nb <= 31), which all belong to table
+// g.t and are no longer than kLongRun. Lane j holds, for run j: its start (my_start, absolute
+// sorted position; lane nb holds the end of the last run) and its row id (my_row).
+template <typename KeyT, typename WT, typename GT, int kVPL>
+__device__ __forceinline__ void stream_runs(const BwdDev& p, const RunGroup& g, uint32_t my_start,
+                                            int64_t my_row, int nb, WarpRing& ring, int lane) {
+  using Row = FloatRow<GT>;
+  const uint32_t p_begin = __shfl_sync(kFullMask, my_start, 0);
+  const int my_off = lane <= nb ? static_cast<int>(my_start - p_begin) : 0x7fffffff;
+  const int total = __shfl_sync(kFullMask, my_off, nb);
+  const int rows_per_stage = min(32, kStageBytes / g.copy_bytes);
+  const int num_stages = (total + rows_per_stage - 1) / rows_per_stage;
+  const bool weighted = p.per_sample_weights != nullptr;
+  const bool mean = p.pooling_mode == B200TBE_POOL_MEAN;
+  const bool scaled = weighted || mean;
+  const uint32_t* vals = p.sorted_vals + p_begin;
+
+  // this lane's run: where its weights and state live; pull them towards L2 now
+  WT* my_w = reinterpret_cast<WT*>(p.dev_weights) + __ldg(p.weights_offsets + g.t) + my_row * g.D;
+  float* my_m = p.optimizer == B200TBE_OPT_ROWWISE_ADAGRAD
+                    ? p.momentum1 + __ldg(p.momentum1_offsets + g.t) + my_row
+                    : nullptr;
+  if (lane < nb) {
+    for (int off = 0; off < g.D * static_cast<int>(sizeof(WT)); off += 128)
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(my_w) + off));
+    if (my_m != nullptr) asm volatile("prefetch.global.L2 [%0];" ::"l"(my_m));
+  }
+
+  Acc4 acc[kVPL];
+#pragma unroll
+  for (int k = 0; k < kVPL; ++k) acc[k].lo = acc[k].hi = make_float2(0.f, 0.f);
+  float bias_unused = 0.f;
+  int cur_run = 0;
+  int cur_end = __shfl_sync(kFullMask, my_off, 1);
+
+  auto flush = [&]() {
+    WT* w_row = reinterpret_cast<WT*>(__shfl_sync(kFullMask, reinterpret_cast<unsigned long long>(my_w), cur_run));
+    float* m_ptr = reinterpret_cast<float*>(__shfl_sync(kFullMask, reinterpret_cast<unsigned long long>(my_m), cur_run));
+    apply_update4<WT, kVPL>(p, acc, w_row, m_ptr, g.D, g.nvec, lane);
+#pragma unroll
+    for (int k = 0; k < kVPL; ++k) acc[k].lo = acc[k].hi = make_float2(0.f, 0.f);
+    ++cur_run;
+    cur_end = __shfl_sync(kFullMask, my_off, (cur_run + 1) & 31);
+  };
+
+  const int chunks = g.copy_bytes >> 4;
+  const int copy_iters = (rows_per_stage * chunks + 31) >> 5;
+  const int lane_row0 = lane / chunks, lane_chunk0 = lane - lane_row0 * chunks;
+  const int row_step = 32 / chunks, chunk_step = 32 - row_step * chunks;
+
+  constexpr int kAhead = 3;
+  uint32_t val_q[kAhead] = {};
+  int issue_pos = lane;
+  int issue_slot = 0;
+  auto load_val = [&](int pos) -> uint32_t {
+    return (lane < rows_per_stage && pos < total) ? __ldg(vals + pos) : kInvalidPayload;
+  };
+  auto issue = [&]() {
+    const int slot = issue_slot;
+    const int pos = issue_pos;
+    const uint32_t payload = val_q[0];
+#pragma unroll
+    for (int q = 0; q + 1 < kAhead; ++q) val_q[q] = val_q[q + 1];
+    val_q[kAhead - 1] = load_val(pos + kAhead * rows_per_stage);
+    issue_pos += rows_per_stage;
+    issue_slot = issue_slot + 1 == kStages ? 0 : issue_slot + 1;
+    const bool ok = lane < rows_per_stage && pos < total && payload != kInvalidPayload;
+    const uint32_t vmask = __ballot_sync(kFullMask, ok);
+    const char* my_src = nullptr;
+    if (ok) {
+      int64_t bag = payload;
+      float w = 1.f;
+      if (weighted) {
+        w = __ldg(p.per_sample_weights + payload);
+        bag = __ldg(p.bag_of_pos + payload);
+      }
+      if (mean) w /= static_cast<float>(bag_length(p, bag));
+      if (scaled) ring.weights[slot][lane] = w;
+      my_src = g.grad_col + (bag - g.bag0) * p.grad_stride * static_cast<int64_t>(sizeof(GT));
+    }
+    if (lane == 0) ring.valid[slot] = vmask;
+    uint32_t dst = smem_u32(ring.rows[slot]) + (lane << 4);
+    int row = lane_row0, chunk = lane_chunk0;
+    for (int it = 0; it < copy_iters; ++it) {
+      const char* src = reinterpret_cast<const char*>(
+          __shfl_sync(kFullMask, reinterpret_cast<unsigned long long>(my_src), row & 31));
+      if (row < rows_per_stage && src != nullptr)
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src + (chunk << 4))
+                     : "memory");
+      row += row_step;
+      chunk += chunk_step;
+      if (chunk >= chunks) {
+        chunk -= chunks;
+        ++row;
+      }
+      dst += 512;
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+
+#pragma unroll
+  for (int q = 0; q < kAhead; ++q) val_q[q] = load_val(lane + q * rows_per_stage);
+  for (int s = 0; s < kStages - 1; ++s) {
+    if (s < num_stages) {
+      issue();
+    } else {
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+  }
+  __syncwarp();
+
+  int slot = 0;
+  int pos0 = 0;
+  for (int stage = 0; stage < num_stages; ++stage) {
+    if (stage + kStages - 1 < num_stages) {
+      issue();
+    } else {
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+    __syncwarp();
+    asm volatile("cp.async.wait_group %0;" ::"n"(kStages - 1) : "memory");
+    __syncwarp();
+    const uint32_t vmask = ring.valid[slot];
+    const int nr = total - pos0 < rows_per_stage ? total - pos0 : rows_per_stage;
+    const uint32_t rows_addr = smem_u32(ring.rows[slot]);
+    uint32_t mult_addr = 0;
+    if (scaled) {
+      ring.mult[slot][lane] = make_float2(((vmask >> lane) & 1u) ? ring.weights[slot][lane] : 0.f, 0.f);
+      mult_addr = smem_u32(ring.mult[slot]);
+      __syncwarp();
+    }
+    const bool all_valid = vmask == (nr == 32 ? 0xffffffffu : ((1u << nr) - 1u));
+    constexpr int kG = kVPL == 1 ? 4 : (kVPL == 2 ? 2 : 1);
+    int r = 0;
+    uint32_t row_addr = rows_addr;
+    uint32_t m_addr = mult_addr;
+    const int m_step = scaled ? 8 : 0;
+    while (r < nr) {
+      const int left_in_run = cur_end - (pos0 + r);
+      if (all_valid && left_in_run >= kG && nr - r >= kG) {
+        consume<Row, kVPL, kG>(acc, bias_unused, row_addr, m_addr, g.copy_bytes, g.nvec, lane);
+        r += kG;
+        row_addr += kG * g.copy_bytes;
+        m_addr += kG * m_step;
+      } else {
+        while (pos0 + r == cur_end) flush();
+        if ((vmask >> r) & 1u)
+          consume<Row, kVPL, 1>(acc, bias_unused, row_addr, m_addr, g.copy_bytes, g.nvec, lane);
+        ++r;
+        row_addr += g.copy_bytes;
+        m_addr += m_step;
+      }
+    }
+    __syncwarp();
+    pos0 += rows_per_stage;
+    slot = slot + 1 == kStages ? 0 : slot + 1;
+  }
+  while (cur_run < nb) flush();
+}
+
+// Persistent, one CTA per SM: warps stride over groups of 31 consecutive runs. A group is cut where
+// the table changes and around runs longer than kLongRun, which are recorded for the chunked path.
+template <typename KeyT, typename WT, typename GT, int kVPL>
+__global__ void __launch_bounds__(kStreamThreads, 1)
+    reduce_runs_stream_kernel(const __grid_constant__ BwdDev p) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  WarpRing* rings = reinterpret_cast<WarpRing*>(smem_raw);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  WarpRing& ring = rings[warp];
+  const int64_t runs = p.counters[0];
+  const int64_t groups = (runs + 30) / 31;
+  const int64_t stride_groups = static_cast<int64_t>(gridDim.x) * kStreamWarps;
+  const KeyT* keys = reinterpret_cast<const KeyT*>(p.sorted_keys);
+  for (int64_t grp = static_cast<int64_t>(blockIdx.x) * kStreamWarps + warp; grp < groups;
+       grp += stride_groups) {
+    const int64_t run0 = grp * 31;
+    const int n_runs = runs - run0 < 31 ? static_cast<int>(runs - run0) : 31;
+    // lane j: start of run j (lane n_runs: end of the last run), its key, table and length
+    const uint32_t my_start = lane <= n_runs ? p.run_start[run0 + lane] : 0u;
+    const uint32_t next_start = __shfl_down_sync(kFullMask, my_start, 1);
+    int my_t = -1;
+    int64_t my_row = 0;
+    bool my_long = false;
+    if (lane < n_runs) {
+      const int64_t key = static_cast<int64_t>(keys[my_start]);
+      int lo = 0, hi = p.T - 1;
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (__ldg(p.hash_size_cumsum + mid) <= key) {
+          lo = mid;
+        } else {
+          hi = mid - 1;
+        }
+      }
+      my_t = lo;
+      my_row = key - __ldg(p.hash_size_cumsum + lo);
+      my_long = next_start - my_start > static_cast<uint32_t>(kLongRun);
+    }
+    if (my_long) {
+      const uint32_t chunks = (next_start - my_start + kLongRun - 1) / kLongRun;
+      const uint32_t slot = atomicAdd(p.counters + 1, 1u);
+      const uint32_t chunk0 = atomicAdd(p.counters + 2, chunks);
+      p.long_run[slot] = static_cast<uint32_t>(run0 + lane);
+      p.long_chunk0[slot] = chunk0;
+      for (uint32_t c = 0; c < chunks; ++c) p.chunk_run[chunk0 + c] = slot;
+    }
+    const uint32_t long_mask = __ballot_sync(kFullMask, my_long);
+    const int prev_t = __shfl_up_sync(kFullMask, my_t, 1);
+    // a new segment starts at lane 0, after a long run, and where the table changes
+    const uint32_t cut_mask = __ballot_sync(
+        kFullMask, lane < n_runs && (lane == 0 || my_t != prev_t || ((long_mask >> (lane - 1)) & 1u)));
+    int a = 0;
+    while (a < n_runs) {
+      if ((long_mask >> a) & 1u) {
+        ++a;
+        continue;
+      }
+      // segment [a, b): up to the next cut or long run
+      const uint32_t later = (cut_mask | long_mask) & ~((2u << a) - 1u);
+      int b = later ? __ffs(later) - 1 : n_runs;
+      if (b > n_runs) b = n_runs;
+      RunGroup g;
+      g.t = __shfl_sync(kFullMask, my_t, a);
+      const int D_begin = __ldg(p.D_offsets + g.t);
+      g.D = __ldg(p.D_offsets + g.t + 1) - D_begin;
+      g.nvec = g.D >> 2;
+      g.copy_bytes = g.D * static_cast<int>(sizeof(GT));
+      g.grad_col = p.grad_output + (p.grad_col_offset + D_begin) * static_cast<int64_t>(sizeof(GT));
+      g.hash0 = 0;
+      g.bag0 = static_cast<int64_t>(g.t) * p.B;
+      const bool ok = (g.copy_bytes & 15) == 0 && (reinterpret_cast<uintptr_t>(g.grad_col) & 15) == 0 &&
+                      g.nvec <= 32 * kVPL && g.copy_bytes <= kStageBytes && g.D > 0;
+      if (ok) {
+        // re-base the lanes so that lane j describes run a + j
+        const uint32_t seg_start = __shfl_sync(kFullMask, my_start, (lane + a) & 31);
+        const int64_t seg_row = __shfl_sync(kFullMask, my_row, (lane + a) & 31);
+        stream_runs<KeyT, WT, GT, kVPL>(p, g, seg_start, seg_row, b - a, ring, lane);
+      } else if (lane == 0 && p.status != nullptr) {
+        atomicOr(p.status, B200TBE_DEV_UNSUPPORTED_SHAPE);
+      }
+      a = b;
+    }
+  }
+}
+
 // Persistent: one warp per chunk of a long run; the chunk's partial row goes to scratch.
 template <typename KeyT, typename GT, int kVPL>
 __global__ void __launch_bounds__(kBwdThreads) reduce_chunks_kernel(BwdDev p) {
@@ -478,7 +776,11 @@ int persistent_grid() {
 template <typename KeyT, typename WT, typename GT, int kVPL>
 int run_reduce(const BwdDev& d, cudaStream_t stream) {
   const int grid = persistent_grid();
-  reduce_runs_kernel<KeyT, WT, GT, kVPL><<<grid, kBwdThreads, 0, stream>>>(d);
+  auto stream_kernel = reduce_runs_stream_kernel<KeyT, WT, GT, kVPL>;
+  if (cudaFuncSetAttribute(stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(kStreamSmemBytes)) != cudaSuccess)
+    return B200TBE_ERR_LAUNCH;
+  stream_kernel<<<kNumSMs, kStreamThreads, kStreamSmemBytes, stream>>>(d);
   reduce_chunks_kernel<KeyT, GT, kVPL><<<grid, kBwdThreads, 0, stream>>>(d);
   finish_long_runs_kernel<KeyT, WT, GT, kVPL><<<grid, kBwdThreads, 0, stream>>>(d);
   return launch_status();

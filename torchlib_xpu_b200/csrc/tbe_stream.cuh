@@ -382,7 +382,7 @@ __device__ __forceinline__ bool stream_unit(const StreamBags& bags, const Stream
   // indices of the lookups this lane will issue in the next kIdxAhead stages: the index loads run
   // that many stages ahead of the row copies, which run kStages - 1 stages ahead of consumption
   constexpr int kIdxAhead = 3;
-  int64_t idx_q[kIdxAhead];
+  int64_t idx_q[kIdxAhead] = {};
 #ifdef B200TBE_STREAM_LDGSTS
   const int chunks = tab.copy_bytes >> 4;                       // 16-byte chunks per row
   const int copy_iters = (rows_per_stage * chunks + 31) >> 5;    // warp instructions per stage
