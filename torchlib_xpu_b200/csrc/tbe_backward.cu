@@ -391,6 +391,70 @@ __device__ __forceinline__ void apply_update4(const BwdDev& p, Acc4 (&acc)[kVPL]
   }
 }
 
+// Weight vector of 4 elements as loaded from global memory, and its update.
+template <typename WT>
+struct WVec4;
+template <>
+struct WVec4<float> {
+  using Raw = uint4;
+  static __device__ __forceinline__ void update_store(float* dst, Raw w, const float (&g)[4], float mult) {
+    float4 x = make_float4(__uint_as_float(w.x), __uint_as_float(w.y), __uint_as_float(w.z),
+                           __uint_as_float(w.w));
+    x.x = fmaf(-mult, g[0], x.x);
+    x.y = fmaf(-mult, g[1], x.y);
+    x.z = fmaf(-mult, g[2], x.z);
+    x.w = fmaf(-mult, g[3], x.w);
+    *reinterpret_cast<float4*>(dst) = x;
+  }
+};
+template <>
+struct WVec4<__half> {
+  using Raw = uint2;
+  static __device__ __forceinline__ void update_store(__half* dst, Raw w, const float (&g)[4], float mult) {
+    float2 a = half2_bits_to_float2(w.x), b = half2_bits_to_float2(w.y);
+    a.x = fmaf(-mult, g[0], a.x);
+    a.y = fmaf(-mult, g[1], a.y);
+    b.x = fmaf(-mult, g[2], b.x);
+    b.y = fmaf(-mult, g[3], b.y);
+    // round to nearest even
+    *reinterpret_cast<uint2*>(dst) = make_uint2(float2_to_half2_bits(a.x, a.y), float2_to_half2_bits(b.x, b.y));
+  }
+};
+
+// Optimizer step for one row whose weights (w_regs) and state (m_old, valid on lane 0) were loaded
+// earlier. Lane v holds elements [4v, 4v+4) of vector k*32+v in acc[k].
+template <typename WT, int kVPL>
+__device__ __forceinline__ void apply_update_preloaded(const BwdDev& p, Acc4 (&acc)[kVPL],
+                                                       typename WVec4<WT>::Raw (&w_regs)[kVPL],
+                                                       float m_old, WT* w_row, float* m_ptr, int D,
+                                                       int nvec, int lane) {
+  float mult = p.learning_rate;
+  if (p.optimizer == B200TBE_OPT_ROWWISE_ADAGRAD) {
+    float sq = 0.f;
+#pragma unroll
+    for (int k = 0; k < kVPL; ++k) {
+      if (k * 32 + lane < nvec) {
+        sq = fmaf(acc[k].lo.x, acc[k].lo.x, sq);
+        sq = fmaf(acc[k].lo.y, acc[k].lo.y, sq);
+        sq = fmaf(acc[k].hi.x, acc[k].hi.x, sq);
+        sq = fmaf(acc[k].hi.y, acc[k].hi.y, sq);
+      }
+    }
+    sq = warp_sum(sq);
+    const float m_new = __shfl_sync(kFullMask, m_old, 0) + sq / static_cast<float>(D);
+    if (lane == 0) *m_ptr = m_new;
+    mult = p.learning_rate / (sqrtf(m_new) + p.eps);
+  }
+#pragma unroll
+  for (int k = 0; k < kVPL; ++k) {
+    const int v = k * 32 + lane;
+    if (v < nvec) {
+      const float g[4] = {acc[k].lo.x, acc[k].lo.y, acc[k].hi.x, acc[k].hi.y};
+      WVec4<WT>::update_store(w_row + 4 * v, w_regs[k], g, mult);
+    }
+  }
+}
+
 struct RunGroup {
   int t;                 // table of every run in the group
   int D;
@@ -436,14 +500,31 @@ __device__ __forceinline__ void stream_runs(const BwdDev& p, const RunGroup& g, 
   int cur_run = 0;
   int cur_end = __shfl_sync(kFullMask, my_off, 1);
 
+  // weights and state of the run being summed are loaded when the run begins, one run ahead of
+  // their use, so the update at the run's end does not wait on them
+  typename WVec4<WT>::Raw w_regs[kVPL];
+  float m_old = 0.f;
+  WT* w_row = nullptr;
+  float* m_ptr = nullptr;
+  auto load_run_state = [&](int run) {
+    w_row = reinterpret_cast<WT*>(__shfl_sync(kFullMask, reinterpret_cast<unsigned long long>(my_w), run));
+    m_ptr = reinterpret_cast<float*>(__shfl_sync(kFullMask, reinterpret_cast<unsigned long long>(my_m), run));
+#pragma unroll
+    for (int k = 0; k < kVPL; ++k) {
+      const int v = k * 32 + lane;
+      if (v < g.nvec) w_regs[k] = *reinterpret_cast<const typename WVec4<WT>::Raw*>(w_row + 4 * v);
+    }
+    if (lane == 0 && m_ptr != nullptr) m_old = *m_ptr;
+  };
+  load_run_state(0);
+
   auto flush = [&]() {
-    WT* w_row = reinterpret_cast<WT*>(__shfl_sync(kFullMask, reinterpret_cast<unsigned long long>(my_w), cur_run));
-    float* m_ptr = reinterpret_cast<float*>(__shfl_sync(kFullMask, reinterpret_cast<unsigned long long>(my_m), cur_run));
-    apply_update4<WT, kVPL>(p, acc, w_row, m_ptr, g.D, g.nvec, lane);
+    apply_update_preloaded<WT, kVPL>(p, acc, w_regs, m_old, w_row, m_ptr, g.D, g.nvec, lane);
 #pragma unroll
     for (int k = 0; k < kVPL; ++k) acc[k].lo = acc[k].hi = make_float2(0.f, 0.f);
     ++cur_run;
     cur_end = __shfl_sync(kFullMask, my_off, (cur_run + 1) & 31);
+    if (cur_run < nb) load_run_state(cur_run);
   };
 
   const int chunks = g.copy_bytes >> 4;
