@@ -121,7 +121,7 @@ def uniform_half_table(num_elems, lo, hi, gen):
 
 
 def backward_launches(bits: int) -> int:
-    passes = (bits + 7) // 8
+    passes = (bits + 9) // 10
     return 1 + passes * 5 + 3 + 3  # linearize, per pass hist+3 scan+scatter, segmentation, reduce
 
 

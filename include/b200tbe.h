@@ -212,7 +212,7 @@ B200TBE_API int b200tbe_radix_sort_pairs(void* keys_in, uint32_t* vals_in, void*
 /* The same sort for callers that cannot allocate device memory when they call it -- a plain C or
  * C++ host with no tensor allocator to borrow scratch from, a server that has already given all of
  * HBM to its tables, a loop that cannot take the device-wide synchronisation of cudaMalloc. The
- * scratch is a fixed array inside the library (about 513 KiB on every GPU that loads it, held
+ * scratch is a fixed array inside the library (about 2 MiB on every GPU that loads it, held
  * until the process exits), so n is limited to b200tbe_radix_sort_pairs_static_max() = 2^20 pairs;
  * larger n returns B200TBE_ERR_TOO_LARGE. The entry point calls no cudaMalloc, cudaFree or other
  * allocating routine. Its first call on a device looks up the array's device address (once per

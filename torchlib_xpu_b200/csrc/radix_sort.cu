@@ -1,6 +1,6 @@
 // Stable least-significant-digit radix sort of (key, 32-bit payload) pairs.
 //
-// One pass per digit of up to 8 bits, three steps per pass, none of which waits on another CTA:
+// One pass per digit of up to 10 bits, three steps per pass, none of which waits on another CTA:
 //   1. per-tile digit histograms (shared-memory counters), stored digit-major: counts[d][tile];
 //   2. an exclusive scan over that matrix read in storage order, which turns each entry into the
 //      global position of the first key of tile `tile` with digit d;
@@ -9,7 +9,7 @@
 //      the tile is reordered by digit in shared memory, and then written out so that keys of one
 //      digit go to consecutive addresses.
 // Keys and payloads are read and written exactly once per pass (plus one extra read of the keys
-// for the histogram); with 25..28-bit keys that is 4 passes.
+// for the histogram); with 25..28-bit keys that is 3 passes.
 #include "radix_sort.cuh"
 #include "scan.cuh"
 
@@ -18,7 +18,9 @@ namespace {
 
 constexpr int kSortThreads = 256;
 constexpr int kSortWarps = kSortThreads / 32;
-constexpr int kMaxRadix = 256;
+constexpr int kMaxRadix = 1024;
+constexpr int kDigitsPerThread = kMaxRadix / kSortThreads;
+constexpr int kMaxDigitBits = 10;
 
 template <typename KeyT>
 struct SortTile {
@@ -33,7 +35,7 @@ __global__ void __launch_bounds__(kSortThreads)
   constexpr int kItems = SortTile<KeyT>::kItems;
   constexpr int kTile = SortTile<KeyT>::kTile;
   __shared__ uint32_t hist[kMaxRadix];
-  hist[threadIdx.x] = 0;
+  for (int d = threadIdx.x; d < kMaxRadix; d += kSortThreads) hist[d] = 0;
   __syncthreads();
   const int64_t base = static_cast<int64_t>(blockIdx.x) * kTile;
 #pragma unroll
@@ -42,8 +44,8 @@ __global__ void __launch_bounds__(kSortThreads)
     if (idx < n) atomicAdd(&hist[static_cast<uint32_t>(keys[idx] >> shift) & mask], 1u);
   }
   __syncthreads();
-  if (threadIdx.x < radix)
-    counts[static_cast<int64_t>(threadIdx.x) * num_tiles + blockIdx.x] = hist[threadIdx.x];
+  for (int d = threadIdx.x; d < radix; d += kSortThreads)
+    counts[static_cast<int64_t>(d) * num_tiles + blockIdx.x] = hist[d];
 }
 
 template <typename KeyT>
@@ -54,11 +56,12 @@ __global__ void __launch_bounds__(kSortThreads)
                         const uint32_t* __restrict__ positions, int num_tiles) {
   constexpr int kItems = SortTile<KeyT>::kItems;
   constexpr int kTile = SortTile<KeyT>::kTile;
-  __shared__ uint32_t warp_hist[kSortWarps][kMaxRadix];
-  __shared__ uint32_t digit_start[kMaxRadix];
-  __shared__ uint32_t delta[kMaxRadix];
-  __shared__ KeyT skeys[kTile];
-  __shared__ uint32_t svals[kTile];
+  extern __shared__ __align__(16) unsigned char sort_smem[];
+  uint32_t(*warp_hist)[kMaxRadix] = reinterpret_cast<uint32_t(*)[kMaxRadix]>(sort_smem);
+  uint32_t* digit_start = reinterpret_cast<uint32_t*>(sort_smem) + kSortWarps * kMaxRadix;
+  uint32_t* delta = digit_start + kMaxRadix;
+  KeyT* skeys = reinterpret_cast<KeyT*>(delta + kMaxRadix);
+  uint32_t* svals = reinterpret_cast<uint32_t*>(skeys + kTile);
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int i = threadIdx.x; i < kSortWarps * kMaxRadix; i += kSortThreads)
@@ -95,23 +98,32 @@ __global__ void __launch_bounds__(kSortThreads)
   }
   __syncthreads();
 
-  // per digit: exclusive prefix over the warps, then over the digits of the tile
-  uint32_t digit_total = 0;
-  {
-    const int d = threadIdx.x;
+  // per digit: exclusive prefix over the warps, then over the digits of the tile; thread i owns
+  // the kDigitsPerThread consecutive digits starting at i * kDigitsPerThread
+  uint32_t totals[kDigitsPerThread];
+  uint32_t thread_total = 0;
+#pragma unroll
+  for (int j = 0; j < kDigitsPerThread; ++j) {
+    const int d = threadIdx.x * kDigitsPerThread + j;
+    uint32_t run = 0;
 #pragma unroll
     for (int w = 0; w < kSortWarps; ++w) {
       const uint32_t c = warp_hist[w][d];
-      warp_hist[w][d] = digit_total;
-      digit_total += c;
+      warp_hist[w][d] = run;
+      run += c;
     }
+    totals[j] = run;
+    thread_total += run;
   }
   uint32_t unused_total;
-  const uint32_t start = block_exclusive_scan(digit_total, &unused_total);
-  digit_start[threadIdx.x] = start;
-  if (threadIdx.x < radix)
-    delta[threadIdx.x] =
-        positions[static_cast<int64_t>(threadIdx.x) * num_tiles + blockIdx.x] - start;
+  uint32_t start = block_exclusive_scan(thread_total, &unused_total);
+#pragma unroll
+  for (int j = 0; j < kDigitsPerThread; ++j) {
+    const int d = threadIdx.x * kDigitsPerThread + j;
+    digit_start[d] = start;
+    if (d < radix) delta[d] = positions[static_cast<int64_t>(d) * num_tiles + blockIdx.x] - start;
+    start += totals[j];
+  }
   __syncthreads();
 
 #pragma unroll
@@ -147,7 +159,12 @@ int sort_impl(KeyT* keys_a, uint32_t* vals_a, KeyT* keys_b, uint32_t* vals_b, in
   const int64_t tiles64 = sort_num_tiles<KeyT>(n);
   if (tiles64 > 0x7fffffff / kMaxRadix) return B200TBE_ERR_TOO_LARGE;
   const int tiles = static_cast<int>(tiles64);
-  const int passes = (key_bits + 7) / 8;
+  const int passes = (key_bits + kMaxDigitBits - 1) / kMaxDigitBits;
+  const size_t scatter_smem = static_cast<size_t>(kSortWarps + 2) * kMaxRadix * 4 +
+                              static_cast<size_t>(SortTile<KeyT>::kTile) * (sizeof(KeyT) + 4);
+  if (cudaFuncSetAttribute(sort_scatter_kernel<KeyT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(scatter_smem)) != cudaSuccess)
+    return B200TBE_ERR_LAUNCH;
   bool in_b = false;
   int shift = 0;
   for (int pass = 0; pass < passes; ++pass) {
@@ -164,7 +181,7 @@ int sort_impl(KeyT* keys_a, uint32_t* vals_a, KeyT* keys_b, uint32_t* vals_b, in
     const int st = exclusive_scan_u32(counts, static_cast<int64_t>(radix) * tiles, tile_sums,
                                       nullptr, stream);
     if (st != B200TBE_OK) return st;
-    sort_scatter_kernel<KeyT><<<tiles, kSortThreads, 0, stream>>>(kin, vin, kout, vout, n, shift,
+    sort_scatter_kernel<KeyT><<<tiles, kSortThreads, scatter_smem, stream>>>(kin, vin, kout, vout, n, shift,
                                                                  mask, radix, counts, tiles);
     in_b = !in_b;
     shift += bits;
@@ -253,8 +270,8 @@ namespace {
 
 constexpr int64_t kStaticSortMaxPairs = int64_t{1} << 20;
 // counts for the narrower (8-byte-key) tile + scan tile sums + slack, as radix_sort_scratch_bytes()
-// computes for kStaticSortMaxPairs: 512 tiles x 256 digits x 4 B = 512 KiB, plus under 1 KiB.
-constexpr size_t kStaticSortScratchBytes = (size_t{512} * 256 * 4) + 1024;
+// computes for kStaticSortMaxPairs: 512 tiles x 1024 digits x 4 B = 2 MiB, plus under 4 KiB.
+constexpr size_t kStaticSortScratchBytes = (size_t{512} * kMaxRadix * 4) + 4096;
 
 static __device__ __align__(256) unsigned char g_static_sort_scratch[kStaticSortScratchBytes];
 

@@ -6,12 +6,14 @@
 //               while one table's rows are being reduced only that table's slice of the gradient
 //               matrix (B x D_t) is live and stays in L2
 //   segment     head flags + compaction give the start of every run of equal keys
-//   reduce      persistent grid, one warp per run: the gradient slices of the run's bags are summed
-//               in sorted order with 16-byte loads (sub-warp groups when a slice is narrower than
-//               512 bytes), then the row and its optimizer state are read, updated and written once.
-//               Runs longer than kLongRun are cut into chunks of kLongRun lookups; a second kernel
-//               reduces each chunk to a partial row in scratch and a third adds a run's partials in
-//               chunk order and applies the update. Summation order is fixed by the data alone.
+//   reduce      persistent grid, one CTA per SM, on the shared-memory ring engine of
+//               tbe_stream.cuh: a warp takes 31 consecutive runs, streams the gradient slices of
+//               their lookups through its ring (cp.async, two stages in flight) and sums them run
+//               by run; weights and state of a run are loaded when the run begins and the row is
+//               updated once, in place, when the stream crosses the run's end. Runs longer than
+//               kLongRun are cut into chunks of kLongRun lookups: a second kernel streams each
+//               chunk the same way into a partial row in scratch and a third adds a run's partials
+//               in chunk order and applies the update. Summation order is fixed by the data alone.
 #include "radix_sort.cuh"
 #include "scan.cuh"
 #include "tbe_stream.cuh"
@@ -129,77 +131,10 @@ __global__ void __launch_bounds__(kSegThreads)
   if (blockIdx.x == 0 && threadIdx.x == 0) run_start[counters[0]] = static_cast<uint32_t>(n);
 }
 
-// ---- gradient accumulation over a range of sorted lookups ------------------------------------
-// Sums, for sorted positions [s, e), the gradient slice of each lookup's bag (scaled by 1/L for
-// MEAN pooling and by the per-sample weight) into acc. Lane (g, v): group g takes every
-// rows_per_step-th lookup, v indexes the 16-byte vector inside the slice.
 __device__ __forceinline__ int64_t bag_length(const BwdDev& p, int64_t bag) {
   if (p.index_bytes == 8)
     return load_index<int64_t>(p.offsets, bag + 1) - load_index<int64_t>(p.offsets, bag);
   return load_index<int32_t>(p.offsets, bag + 1) - load_index<int32_t>(p.offsets, bag);
-}
-
-template <typename GT, int kVPL>
-__device__ __forceinline__ void accumulate_range(const BwdDev& p, float (&acc)[kVPL][RowVec<GT>::kElems],
-                                                 int64_t s, int64_t e, int t, int gs, int slice_vecs,
-                                                 const char* grad_col, int lane) {
-  constexpr int kUnroll = kVPL == 1 ? 4 : (kVPL == 2 ? 2 : 1);
-  const int rows_per_step = 32 / gs;
-  const int g = lane / gs;
-  const int v = lane - g * gs;
-  const bool mean = p.pooling_mode == B200TBE_POOL_MEAN;
-  const bool weighted = p.per_sample_weights != nullptr;
-  const int64_t bag0 = static_cast<int64_t>(t) * p.B;
-  for (int64_t c = s; c < e; c += 32) {
-    const int n = e - c < 32 ? static_cast<int>(e - c) : 32;
-    int64_t my_row = -1;  // batch row of this lane's lookup
-    float my_w = 1.f;
-    if (lane < n) {
-      uint32_t payload = __ldg(p.sorted_vals + c + lane);
-      if (payload != kInvalidPayload) {
-        int64_t bag;
-        if (weighted) {
-          my_w = __ldg(p.per_sample_weights + payload);
-          bag = __ldg(p.bag_of_pos + payload);
-        } else {
-          bag = payload;
-        }
-        my_row = bag - bag0;
-        if (mean) my_w /= static_cast<float>(bag_length(p, bag));
-      }
-    }
-    for (int j = 0; j < n; j += rows_per_step * kUnroll) {
-      uint4 buf[kUnroll][kVPL];
-      float w[kUnroll];
-      bool ok[kUnroll];
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        const int rr = j + u * rows_per_step + g;
-        const int64_t row = __shfl_sync(kFullMask, my_row, rr & 31);
-        w[u] = __shfl_sync(kFullMask, my_w, rr & 31);
-        ok[u] = rr < n && row >= 0;
-        if (ok[u]) {
-          const char* src = grad_col + row * p.grad_stride * static_cast<int64_t>(sizeof(GT));
-#pragma unroll
-          for (int k = 0; k < kVPL; ++k) {
-            const int vv = k * 32 + v;
-            if (vv < slice_vecs) buf[u][k] = ldg_stream16(src + (static_cast<int64_t>(vv) << 4));
-          }
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        if (ok[u]) {
-#pragma unroll
-          for (int k = 0; k < kVPL; ++k) {
-            if (k * 32 + v < slice_vecs) {
-              RowVec<GT>::fma(acc[k], buf[u][k], w[u]);  // w is exactly 1 when unweighted
-            }
-          }
-        }
-      }
-    }
-  }
 }
 
 template <typename WT>
@@ -266,14 +201,6 @@ __device__ __forceinline__ void apply_update(const BwdDev& p, float (&acc)[kVPL]
   }
 }
 
-template <int kE, int kVPL>
-__device__ __forceinline__ void combine_groups(float (&acc)[kVPL][kE], int gs) {
-  for (int o = 16; o >= gs; o >>= 1) {
-#pragma unroll
-    for (int e = 0; e < kE; ++e) acc[0][e] += __shfl_xor_sync(kFullMask, acc[0][e], o);
-  }
-}
-
 struct RunInfo {
   int t;
   int64_t row;
@@ -309,43 +236,6 @@ __device__ __forceinline__ RunInfo describe_run(const BwdDev& p, int64_t s, int 
          (reinterpret_cast<uintptr_t>(r.grad_col) & 15) == 0 && r.slice_vecs <= 32 * max_vpl;
   if (!r.ok && p.status != nullptr) atomicOr(p.status, B200TBE_DEV_UNSUPPORTED_SHAPE);
   return r;
-}
-
-// Persistent: warps stride over the runs. Short runs are finished here; long runs are recorded.
-template <typename KeyT, typename WT, typename GT, int kVPL>
-__global__ void __launch_bounds__(kBwdThreads) reduce_runs_kernel(BwdDev p) {
-  constexpr int kE = RowVec<GT>::kElems;
-  const int lane = threadIdx.x & 31;
-  const int64_t warp0 = static_cast<int64_t>(blockIdx.x) * kBwdWarps + (threadIdx.x >> 5);
-  const int64_t num_warps = static_cast<int64_t>(gridDim.x) * kBwdWarps;
-  const int64_t runs = p.counters[0];
-  for (int64_t run = warp0; run < runs; run += num_warps) {
-    const int64_t s = p.run_start[run], e = p.run_start[run + 1];
-    if (e - s > kLongRun) {
-      const uint32_t chunks = static_cast<uint32_t>((e - s + kLongRun - 1) / kLongRun);
-      uint32_t slot = 0, chunk0 = 0;
-      if (lane == 0) {
-        slot = atomicAdd(p.counters + 1, 1u);
-        chunk0 = atomicAdd(p.counters + 2, chunks);
-        p.long_run[slot] = static_cast<uint32_t>(run);
-        p.long_chunk0[slot] = chunk0;
-      }
-      chunk0 = __shfl_sync(kFullMask, chunk0, 0);
-      slot = __shfl_sync(kFullMask, slot, 0);
-      for (uint32_t c = lane; c < chunks; c += 32) p.chunk_run[chunk0 + c] = slot;
-      continue;
-    }
-    const RunInfo r = describe_run<KeyT, GT>(p, s, kVPL);
-    if (!r.ok) continue;
-    float acc[kVPL][kE];
-#pragma unroll
-    for (int k = 0; k < kVPL; ++k)
-#pragma unroll
-      for (int i = 0; i < kE; ++i) acc[k][i] = 0.f;
-    accumulate_range<GT, kVPL>(p, acc, s, e, r.t, r.gs, r.slice_vecs, r.grad_col, lane);
-    combine_groups<kE, kVPL>(acc, r.gs);
-    apply_update<WT, kE, kVPL>(p, acc, r.t, r.row, r.D, r.gs, r.slice_vecs, lane);
-  }
 }
 
 // ---- streaming reduction of runs -------------------------------------------------------------
@@ -470,7 +360,8 @@ struct RunGroup {
 // sorted position; lane nb holds the end of the last run) and its row id (my_row).
 template <typename KeyT, typename WT, typename GT, int kVPL>
 __device__ __forceinline__ void stream_runs(const BwdDev& p, const RunGroup& g, uint32_t my_start,
-                                            int64_t my_row, int nb, WarpRing& ring, int lane) {
+                                            int64_t my_row, int nb, WarpRing& ring, int lane,
+                                            float* partial_dst = nullptr) {
   using Row = FloatRow<GT>;
   const uint32_t p_begin = __shfl_sync(kFullMask, my_start, 0);
   const int my_off = lane <= nb ? static_cast<int>(my_start - p_begin) : 0x7fffffff;
@@ -487,7 +378,7 @@ __device__ __forceinline__ void stream_runs(const BwdDev& p, const RunGroup& g, 
   float* my_m = p.optimizer == B200TBE_OPT_ROWWISE_ADAGRAD
                     ? p.momentum1 + __ldg(p.momentum1_offsets + g.t) + my_row
                     : nullptr;
-  if (lane < nb) {
+  if (lane < nb && partial_dst == nullptr) {
     for (int off = 0; off < g.D * static_cast<int>(sizeof(WT)); off += 128)
       asm volatile("prefetch.global.L2 [%0];" ::"l"(reinterpret_cast<const char*>(my_w) + off));
     if (my_m != nullptr) asm volatile("prefetch.global.L2 [%0];" ::"l"(my_m));
@@ -516,15 +407,26 @@ __device__ __forceinline__ void stream_runs(const BwdDev& p, const RunGroup& g, 
     }
     if (lane == 0 && m_ptr != nullptr) m_old = *m_ptr;
   };
-  load_run_state(0);
+  if (partial_dst == nullptr) load_run_state(0);
 
   auto flush = [&]() {
-    apply_update_preloaded<WT, kVPL>(p, acc, w_regs, m_old, w_row, m_ptr, g.D, g.nvec, lane);
+    if (partial_dst != nullptr) {
+      // a chunk of a long run: its sum goes to scratch, the update happens once all chunks are in
+#pragma unroll
+      for (int k = 0; k < kVPL; ++k) {
+        const int v = k * 32 + lane;
+        if (v < g.nvec)
+          *reinterpret_cast<float4*>(partial_dst + 4 * v) =
+              make_float4(acc[k].lo.x, acc[k].lo.y, acc[k].hi.x, acc[k].hi.y);
+      }
+    } else {
+      apply_update_preloaded<WT, kVPL>(p, acc, w_regs, m_old, w_row, m_ptr, g.D, g.nvec, lane);
+    }
 #pragma unroll
     for (int k = 0; k < kVPL; ++k) acc[k].lo = acc[k].hi = make_float2(0.f, 0.f);
     ++cur_run;
     cur_end = __shfl_sync(kFullMask, my_off, (cur_run + 1) & 31);
-    if (cur_run < nb) load_run_state(cur_run);
+    if (cur_run < nb && partial_dst == nullptr) load_run_state(cur_run);
   };
 
   const int chunks = g.copy_bytes >> 4;
@@ -727,44 +629,49 @@ __global__ void __launch_bounds__(kStreamThreads, 1)
   }
 }
 
-// Persistent: one warp per chunk of a long run; the chunk's partial row goes to scratch.
-template <typename KeyT, typename GT, int kVPL>
-__global__ void __launch_bounds__(kBwdThreads) reduce_chunks_kernel(BwdDev p) {
-  constexpr int kE = RowVec<GT>::kElems;
-  const int lane = threadIdx.x & 31;
-  const int64_t warp0 = static_cast<int64_t>(blockIdx.x) * kBwdWarps + (threadIdx.x >> 5);
-  const int64_t num_warps = static_cast<int64_t>(gridDim.x) * kBwdWarps;
+// Persistent, one CTA per SM: one warp per chunk of a long run, streamed through the ring like a
+// short run; the chunk's sum goes to scratch.
+template <typename KeyT, typename WT, typename GT, int kVPL>
+__global__ void __launch_bounds__(kStreamThreads, 1)
+    reduce_chunks_stream_kernel(const __grid_constant__ BwdDev p) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  WarpRing* rings = reinterpret_cast<WarpRing*>(smem_raw);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  WarpRing& ring = rings[warp];
   const int64_t chunks = p.counters[2];
-  for (int64_t c = warp0; c < chunks; c += num_warps) {
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kStreamWarps;
+  const KeyT* keys = reinterpret_cast<const KeyT*>(p.sorted_keys);
+  for (int64_t c = static_cast<int64_t>(blockIdx.x) * kStreamWarps + warp; c < chunks; c += stride) {
     const uint32_t slot = p.chunk_run[c];
     const uint32_t run = p.long_run[slot];
     const int64_t first = p.long_chunk0[slot];
-    const int64_t s_run = p.run_start[run], e_run = p.run_start[run + 1];
-    const int64_t s = s_run + (c - first) * kLongRun;
-    const int64_t e = s + kLongRun < e_run ? s + kLongRun : e_run;
-    const RunInfo r = describe_run<KeyT, GT>(p, s_run, kVPL);
-    if (!r.ok) continue;
-    float acc[kVPL][kE];
-#pragma unroll
-    for (int k = 0; k < kVPL; ++k)
-#pragma unroll
-      for (int i = 0; i < kE; ++i) acc[k][i] = 0.f;
-    accumulate_range<GT, kVPL>(p, acc, s, e, r.t, r.gs, r.slice_vecs, r.grad_col, lane);
-    combine_groups<kE, kVPL>(acc, r.gs);
-    const int g = lane / r.gs, v = lane - g * r.gs;
-    if (g == 0) {
-      float* dst = p.partials + c * p.max_D;
-#pragma unroll
-      for (int k = 0; k < kVPL; ++k) {
-        const int vv = k * 32 + v;
-        if (vv < r.slice_vecs) {
-#pragma unroll
-          for (int i = 0; i < kE; i += 4)
-            *reinterpret_cast<float4*>(dst + vv * kE + i) =
-                make_float4(acc[k][i], acc[k][i + 1], acc[k][i + 2], acc[k][i + 3]);
-        }
+    const uint32_t s_run = p.run_start[run], e_run = p.run_start[run + 1];
+    const uint32_t s = s_run + static_cast<uint32_t>(c - first) * kLongRun;
+    const uint32_t e = s + kLongRun < e_run ? s + kLongRun : e_run;
+    const int64_t key = static_cast<int64_t>(keys[s_run]);
+    int lo = 0, hi = p.T - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (__ldg(p.hash_size_cumsum + mid) <= key) {
+        lo = mid;
+      } else {
+        hi = mid - 1;
       }
     }
+    RunGroup g;
+    g.t = lo;
+    const int D_begin = __ldg(p.D_offsets + g.t);
+    g.D = __ldg(p.D_offsets + g.t + 1) - D_begin;
+    g.nvec = g.D >> 2;
+    g.copy_bytes = g.D * static_cast<int>(sizeof(GT));
+    g.grad_col = p.grad_output + (p.grad_col_offset + D_begin) * static_cast<int64_t>(sizeof(GT));
+    g.hash0 = 0;
+    g.bag0 = static_cast<int64_t>(g.t) * p.B;
+    const bool ok = (g.copy_bytes & 15) == 0 && (reinterpret_cast<uintptr_t>(g.grad_col) & 15) == 0 &&
+                    g.nvec <= 32 * kVPL && g.copy_bytes <= kStageBytes && g.D > 0;
+    if (!ok) continue;  // flagged by the kernel that recorded the run
+    const uint32_t my_start = lane == 0 ? s : e;
+    stream_runs<KeyT, WT, GT, kVPL>(p, g, my_start, 0, 1, ring, lane, p.partials + c * p.max_D);
   }
 }
 
@@ -862,7 +769,11 @@ int run_reduce(const BwdDev& d, cudaStream_t stream) {
                            static_cast<int>(kStreamSmemBytes)) != cudaSuccess)
     return B200TBE_ERR_LAUNCH;
   stream_kernel<<<kNumSMs, kStreamThreads, kStreamSmemBytes, stream>>>(d);
-  reduce_chunks_kernel<KeyT, GT, kVPL><<<grid, kBwdThreads, 0, stream>>>(d);
+  auto chunk_kernel = reduce_chunks_stream_kernel<KeyT, WT, GT, kVPL>;
+  if (cudaFuncSetAttribute(chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(kStreamSmemBytes)) != cudaSuccess)
+    return B200TBE_ERR_LAUNCH;
+  chunk_kernel<<<kNumSMs, kStreamThreads, kStreamSmemBytes, stream>>>(d);
   finish_long_runs_kernel<KeyT, WT, GT, kVPL><<<grid, kBwdThreads, 0, stream>>>(d);
   return launch_status();
 }
