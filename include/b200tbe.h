@@ -227,6 +227,24 @@ B200TBE_API int b200tbe_radix_sort_pairs_static(void* keys_in, uint32_t* vals_in
                                                 int32_t key_bits, b200tbe_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Row-wise min-max quantisation to INT8 / INT4 / INT2 with an fp16 {scale, bias} pair per row, and
+ * back (torch.ops.fbgemm.FloatOrHalfToFusedNBitRowwiseQuantizedSBHalf and
+ * torch.ops.fbgemm.FusedNBitRowwiseQuantizedSBHalfToFloatOrHalf; arithmetic of FBGEMM
+ * include/fbgemm/QuantUtils.h:277-308). scale = (max - bias) / (2^bits - 1) and bias = min, both
+ * rounded to fp16 first; q = rint((x - bias) / scale), clamped; a zero range stores scale 1.
+ * header_first = 1 gives the table layout b200tbe_nbit_forward reads (header, payload, padding to
+ * row_alignment); header_first = 0 with row_alignment = 1 gives FBGEMM's op layout (payload, header).
+ * src / dst of the float side are [rows, D] contiguous, src_dtype / dst_dtype FP32 or FP16.
+ * ---------------------------------------------------------------------------------------------- */
+B200TBE_API int64_t b200tbe_quantized_row_bytes(int32_t D, int32_t ty, int32_t row_alignment);
+B200TBE_API int b200tbe_quantize_rows(const void* src, int32_t src_dtype, int64_t rows, int32_t D,
+                                      int32_t ty, int32_t row_alignment, int32_t header_first,
+                                      uint8_t* dst, b200tbe_stream_t stream);
+B200TBE_API int b200tbe_dequantize_rows(const uint8_t* src, int64_t rows, int32_t D, int32_t ty,
+                                        int32_t row_alignment, int32_t header_first, void* dst,
+                                        int32_t dst_dtype, b200tbe_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Gradient exchange of the table-wise-sharded configuration (the step a sharded caller runs between
  * its dense part and b200tbe_backward; the pooled rows travel the other way inside b200tbe_forward,
  * which can scatter into peer-mapped destination buffers). Source s is a peer's gradient matrix

@@ -89,7 +89,8 @@ EXPORTS = (
     "b200tbe_status_string", "b200tbe_abi_version", "b200tbe_forward", "b200tbe_nbit_forward",
     "b200tbe_backward_scratch_bytes", "b200tbe_backward", "b200tbe_radix_sort_scratch_bytes",
     "b200tbe_radix_sort_pairs", "b200tbe_radix_sort_pairs_static_max",
-    "b200tbe_radix_sort_pairs_static", "b200tbe_exchange_pull", "b200tbe_jagged_to_padded_dense", "b200tbe_dense_to_jagged",
+    "b200tbe_radix_sort_pairs_static", "b200tbe_exchange_pull", "b200tbe_quantized_row_bytes",
+    "b200tbe_quantize_rows", "b200tbe_dequantize_rows", "b200tbe_jagged_to_padded_dense", "b200tbe_dense_to_jagged",
     "b200tbe_jagged_dense_elementwise_add",
 )
 
@@ -126,6 +127,14 @@ def lib() -> ctypes.CDLL:
             _c_void_p, _c_void_p, _c_void_p, _c_void_p, ctypes.c_int64, ctypes.c_int32,
             ctypes.c_int32, _c_void_p]
         _lib.b200tbe_exchange_pull.argtypes = [ctypes.POINTER(ExchangePullParams), _c_void_p]
+        _lib.b200tbe_quantized_row_bytes.restype = ctypes.c_int64
+        _lib.b200tbe_quantized_row_bytes.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
+        _lib.b200tbe_quantize_rows.argtypes = [
+            _c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+            ctypes.c_int32, _c_void_p, _c_void_p]
+        _lib.b200tbe_dequantize_rows.argtypes = [
+            _c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
+            _c_void_p, ctypes.c_int32, _c_void_p]
         _lib.b200tbe_forward.argtypes = [ctypes.POINTER(ForwardParams), _c_void_p]
         _lib.b200tbe_nbit_forward.argtypes = [ctypes.POINTER(NbitForwardParams), _c_void_p]
         _lib.b200tbe_backward.argtypes = [ctypes.POINTER(BackwardParams), _c_void_p]
@@ -278,6 +287,28 @@ def exchange_pull(src_ptrs, dst, src_stride_bytes, src_col_offset_bytes, rows_pe
     p.dst_stride_bytes = dst.stride(0) * dst.element_size()
     p.rows_per_src, p.row_bytes, p.num_srcs = rows_per_src, row_bytes, len(src_ptrs)
     check(lib().b200tbe_exchange_pull(ctypes.byref(p), _stream()), "b200tbe_exchange_pull")
+
+
+def quantize_rows(src, ty, row_alignment=16, header_first=True):
+    """fp32/fp16 [rows, D] -> uint8 [rows, stride] row-wise quantised (b200tbe_quantize_rows)."""
+    rows, D = src.shape
+    stride = int(lib().b200tbe_quantized_row_bytes(D, ty, row_alignment))
+    if stride < 0:
+        raise B200TbeError("unsupported quantised type %r" % (ty,))
+    dst = torch.empty((rows, stride), dtype=torch.uint8, device=src.device)
+    check(lib().b200tbe_quantize_rows(_p(src), _TORCH_TO_CODE[src.dtype], rows, D, ty, row_alignment,
+                                      int(header_first), _p(dst), _stream()), "b200tbe_quantize_rows")
+    return dst
+
+
+def dequantize_rows(rows_u8, D, ty, row_alignment=16, header_first=True, dtype=torch.float32):
+    """uint8 [rows, stride] -> fp32/fp16 [rows, D] (b200tbe_dequantize_rows)."""
+    rows = rows_u8.shape[0]
+    out = torch.empty((rows, D), dtype=dtype, device=rows_u8.device)
+    check(lib().b200tbe_dequantize_rows(_p(rows_u8), rows, D, ty, row_alignment, int(header_first),
+                                        _p(out), _TORCH_TO_CODE[dtype], _stream()),
+          "b200tbe_dequantize_rows")
+    return out
 
 
 def _jagged_shape(offsets_list, max_lengths, outer, inner, total_rows, elem_bytes, dtype_code):

@@ -467,6 +467,55 @@ Tensor int_nbit_split_embedding_codegen_lookup_function(
   return out;
 }
 
+// ---- fused N-bit row-wise quantisation ops -----------------------------------------------------
+// Layout of FBGEMM's fused N-bit row-wise ops: [rows, payload + 4], fp16 scale and bias BEHIND the
+// payload, rows unpadded.
+
+int nbit_type(int64_t bit_rate) {
+  TORCH_CHECK(bit_rate == 2 || bit_rate == 4 || bit_rate == 8, "bit_rate must be 2, 4 or 8");
+  return bit_rate == 8 ? B200TBE_INT8 : (bit_rate == 4 ? B200TBE_INT4 : B200TBE_INT2);
+}
+
+Tensor float_or_half_to_fused_nbit(const Tensor& input, int64_t bit_rate) {
+  check_cuda_contig(input, "input");
+  TORCH_CHECK(input.dim() == 2, "input must be [rows, columns]");
+  TORCH_CHECK(input.scalar_type() == at::kFloat || input.scalar_type() == at::kHalf,
+              "input must be float32 or float16");
+  const int ty = nbit_type(bit_rate);
+  const int64_t rows = input.size(0), D = input.size(1);
+  TORCH_CHECK(D % (8 / bit_rate) == 0, "columns must be a multiple of ", 8 / bit_rate);
+  c10::cuda::CUDAGuard guard(input.device());
+  const int64_t stride = b200tbe_quantized_row_bytes(static_cast<int32_t>(D), ty, 1);
+  Tensor out = at::empty({rows, stride}, input.options().dtype(at::kByte));
+  check_status(b200tbe_quantize_rows(input.data_ptr(), dtype_code(input.scalar_type()), rows,
+                                     static_cast<int32_t>(D), ty, 1, /*header_first=*/0,
+                                     out.data_ptr<uint8_t>(), current_stream()),
+               "FloatOrHalfToFusedNBitRowwiseQuantizedSBHalf");
+  return out;
+}
+
+Tensor fused_nbit_to_float_or_half(const Tensor& input, int64_t bit_rate, int64_t output_dtype) {
+  check_cuda_contig(input, "input");
+  TORCH_CHECK(input.dim() == 2 && input.scalar_type() == at::kByte, "input must be uint8 [rows, bytes]");
+  TORCH_CHECK(input.size(1) >= 4, "rows must hold the 4-byte scale/bias");
+  const int ty = nbit_type(bit_rate);
+  const int64_t rows = input.size(0), D = (input.size(1) - 4) * (8 / bit_rate);
+  c10::cuda::CUDAGuard guard(input.device());
+  Tensor out = at::empty({rows, D}, input.options().dtype(output_scalar_type(output_dtype)));
+  check_status(b200tbe_dequantize_rows(input.data_ptr<uint8_t>(), rows, static_cast<int32_t>(D), ty,
+                                       1, /*header_first=*/0, out.data_ptr(),
+                                       static_cast<int32_t>(output_dtype), current_stream()),
+               "FusedNBitRowwiseQuantizedSBHalfToFloatOrHalf");
+  return out;
+}
+
+Tensor fused_nbit_to_float(const Tensor& input, int64_t bit_rate) {
+  return fused_nbit_to_float_or_half(input, bit_rate, B200TBE_FP32);
+}
+Tensor fused_nbit_to_half(const Tensor& input, int64_t bit_rate) {
+  return fused_nbit_to_float_or_half(input, bit_rate, B200TBE_FP16);
+}
+
 }  // namespace
 
 // A second definition of these schemas (an fbgemm_gpu install in the same process) makes
@@ -478,6 +527,14 @@ TORCH_LIBRARY_FRAGMENT(fbgemm, m) {
   m.def("dense_to_jagged(Tensor dense, Tensor[] x_offsets, int? total_L=None) -> (Tensor, Tensor[])");
   m.def("jagged_dense_elementwise_add(Tensor x_values, Tensor[] x_offsets, Tensor y) -> Tensor");
   m.def("jagged_2d_to_dense(Tensor values, Tensor offsets, int max_sequence_length) -> Tensor");
+  m.def("FloatToFusedNBitRowwiseQuantizedSBHalf(Tensor input, int bit_rate) -> Tensor");
+  m.def("HalfToFusedNBitRowwiseQuantizedSBHalf(Tensor input, int bit_rate) -> Tensor");
+  m.def("FloatOrHalfToFusedNBitRowwiseQuantizedSBHalf(Tensor input, int bit_rate) -> Tensor");
+  m.def("FusedNBitRowwiseQuantizedSBHalfToFloat(Tensor input, int bit_rate) -> Tensor");
+  m.def("FusedNBitRowwiseQuantizedSBHalfToHalf(Tensor input, int bit_rate) -> Tensor");
+  m.def(
+      "FusedNBitRowwiseQuantizedSBHalfToFloatOrHalf(Tensor input, int bit_rate, int output_dtype=0) "
+      "-> Tensor");
   m.def(
       "split_embedding_codegen_lookup_rowwise_adagrad_function(Tensor placeholder_autograd_tensor, "
       "Tensor dev_weights, Tensor uvm_weights, Tensor lxu_cache_weights, Tensor weights_placements, "
@@ -511,6 +568,12 @@ TORCH_LIBRARY_IMPL(fbgemm, CUDA, m) {
   m.impl("dense_to_jagged", TORCH_FN(dense_to_jagged));
   m.impl("jagged_dense_elementwise_add", TORCH_FN(jagged_dense_elementwise_add));
   m.impl("jagged_2d_to_dense", TORCH_FN(jagged_2d_to_dense));
+  m.impl("FloatToFusedNBitRowwiseQuantizedSBHalf", TORCH_FN(float_or_half_to_fused_nbit));
+  m.impl("HalfToFusedNBitRowwiseQuantizedSBHalf", TORCH_FN(float_or_half_to_fused_nbit));
+  m.impl("FloatOrHalfToFusedNBitRowwiseQuantizedSBHalf", TORCH_FN(float_or_half_to_fused_nbit));
+  m.impl("FusedNBitRowwiseQuantizedSBHalfToFloat", TORCH_FN(fused_nbit_to_float));
+  m.impl("FusedNBitRowwiseQuantizedSBHalfToHalf", TORCH_FN(fused_nbit_to_half));
+  m.impl("FusedNBitRowwiseQuantizedSBHalfToFloatOrHalf", TORCH_FN(fused_nbit_to_float_or_half));
   m.impl("int_nbit_split_embedding_codegen_lookup_function",
          TORCH_FN(int_nbit_split_embedding_codegen_lookup_function));
 }
