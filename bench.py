@@ -199,6 +199,10 @@ class ShardedTbeStep:
                       cabi.OPT_ROWWISE_ADAGRAD, 0.01, 1e-8, self.momentum, self.momentum_offsets,
                       scratch=self.scratch)
 
+    def result(self):
+        """Pooled rows this rank ends the forward with (its batch slice, all tables, when sharded)."""
+        return self.pooled if self.exchange is None else self.exchange.recv
+
     def step(self):
         self.forward()
         self.backward()
@@ -488,17 +492,19 @@ def main():
     # ---- end to end: host buffers in, pooled rows out, every step ---------------------------
     h_idx = step.indices.cpu().pin_memory()
     h_off = step.offsets.cpu().pin_memory()
-    h_grad = step.grad.cpu().pin_memory()
-    h_out = torch.empty(step.pooled.shape, dtype=step.pooled.dtype).pin_memory()
-    h2d = h_idx.numel() * 8 + h_off.numel() * 8 + h_grad.numel() * h_grad.element_size()
-    d2h = h_out.numel() * h_out.element_size()
+    grad_in = step.grad if step.exchange is None else step.exchange.grad_slice
+    h_grad = grad_in.cpu().pin_memory()
+    h_out = torch.empty(step.result().shape, dtype=step.result().dtype).pin_memory()
+    # whole-job bytes: every rank copies its own inputs and its own slice of the result
+    h2d = (h_idx.numel() * 8 + h_off.numel() * 8 + h_grad.numel() * h_grad.element_size()) * world
+    d2h = h_out.numel() * h_out.element_size() * world
 
     def e2e_step():
         step.indices.copy_(h_idx, non_blocking=True)
         step.offsets.copy_(h_off, non_blocking=True)
         step.forward()
-        h_out.copy_(step.pooled, non_blocking=True)
-        step.grad.copy_(h_grad, non_blocking=True)
+        h_out.copy_(step.result(), non_blocking=True)
+        grad_in.copy_(h_grad, non_blocking=True)
         step.backward()
 
     e2e_step()
