@@ -249,7 +249,7 @@ def cpu_sample_rate(cfg, budget_s=12.0):
     return inp.num_lookups * reps / dt, threads, sample, dt / reps
 
 
-def reference_arm(args, cfg, rank):
+def reference_arm(args, cfg, rank, json_out):
     if rank != 0:
         return
     steps, warm = args.steps, args.warmup
@@ -265,7 +265,7 @@ def reference_arm(args, cfg, rank):
                          "sample": sample},
         "e2e": {"value": rate, "unit": "lookups/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line))
+    print(json.dumps(line), file=json_out, flush=True)
 
 
 # --------------------------------------------------------------------------------------------
@@ -400,7 +400,17 @@ def _bench_nbit(entry, flush, gen, iters):
     entry("tbe_nbit_forward(config4)", bytes_, ms, inp.num_lookups, {"unique_rows": int(sum(U_by_table))})
 
 
+def _claim_stdout():
+    """Libraries (NCCL among them) print banners on stdout; the contract is ONE JSON line there. Point
+    fd 1 at stderr for the run and hand back a file on the original stdout for the final line."""
+    sys.stdout.flush()
+    keep = os.dup(1)
+    os.dup2(2, 1)
+    return os.fdopen(keep, "w")
+
+
 def main():
+    json_out = _claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
@@ -422,7 +432,7 @@ def main():
     cfg = workloads.CONFIGS["tbe_sharded"]
 
     if args.impl == "reference":
-        reference_arm(args, cfg, rank)
+        reference_arm(args, cfg, rank, json_out)
         return
 
     if not torch.cuda.is_available():
@@ -439,7 +449,7 @@ def main():
         global TABLES_OVERRIDE
         TABLES_OVERRIDE = args.tables
         print(json.dumps({"only": args.only, "peak_gbs": peak_gbs,
-                          "results": bench_others(peak_gbs, args.iters, args.only)}))
+                          "results": bench_others(peak_gbs, args.iters, args.only)}), file=json_out, flush=True)
         return
 
     step = ShardedTbeStep(rank, world, cfg, small=args.small)
@@ -572,7 +582,7 @@ def main():
             line["cpu_baseline"] = {"value": None, "unit": "lookups/s", "cores": None, "kind": "reference",
                                     "sample": "failed: %r" % (exc,)}
     if rank == 0:
-        print(json.dumps(line))
+        print(json.dumps(line), file=json_out, flush=True)
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
