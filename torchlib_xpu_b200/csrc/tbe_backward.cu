@@ -6,14 +6,15 @@
 //               while one table's rows are being reduced only that table's slice of the gradient
 //               matrix (B x D_t) is live and stays in L2
 //   segment     head flags + compaction give the start of every run of equal keys
-//   reduce      persistent grid, one CTA per SM, on the shared-memory ring engine of
-//               tbe_stream.cuh: a warp takes 31 consecutive runs, streams the gradient slices of
-//               their lookups through its ring (cp.async, two stages in flight) and sums them run
-//               by run; weights and state of a run are loaded when the run begins and the row is
-//               updated once, in place, when the stream crosses the run's end. Runs longer than
-//               kLongRun are cut into chunks of kLongRun lookups: a second kernel streams each
-//               chunk the same way into a partial row in scratch and a third adds a run's partials
-//               in chunk order and applies the update. Summation order is fixed by the data alone.
+//   reduce      rows of up to 512 elements: tbe_backward_runs.cuh, a plain grid at high occupancy;
+//               a warp owns 32 consecutive runs, a group of lanes sums one run's gradient slices in
+//               registers and updates the row once, in place. Wider rows: persistent grid, one CTA
+//               per SM, on the shared-memory ring engine of tbe_stream.cuh (a warp takes 31
+//               consecutive runs and streams the gradient slices of their lookups through its ring).
+//               Runs longer than kLongRun are cut into chunks of kLongRun lookups: a second kernel
+//               streams each chunk through the ring into a partial row in scratch and a third adds a
+//               run's partials in chunk order and applies the update. Summation order is fixed by
+//               the data alone.
 #include "radix_sort.cuh"
 #include "scan.cuh"
 #include "tbe_stream.cuh"
@@ -344,6 +345,8 @@ __device__ __forceinline__ void apply_update_preloaded(const BwdDev& p, Acc4 (&a
     }
   }
 }
+
+#include "tbe_backward_runs.cuh"
 
 struct RunGroup {
   int t;                 // table of every run in the group
@@ -768,7 +771,19 @@ int run_reduce(const BwdDev& d, cudaStream_t stream) {
   if (cudaFuncSetAttribute(stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(kStreamSmemBytes)) != cudaSuccess)
     return B200TBE_ERR_LAUNCH;
-  stream_kernel<<<kNumSMs, kStreamThreads, kStreamSmemBytes, stream>>>(d);
+  if (d.max_D <= 512) {
+    // one warp per 32 runs; the run count is known on the device only, num_indices bounds it
+    const int64_t ctas = (d.num_indices + 32 * kRunWarps - 1) / (32 * kRunWarps);
+    if (ctas > 0x7fffffff) return B200TBE_ERR_TOO_LARGE;
+    const unsigned run_grid = static_cast<unsigned>(ctas > 0 ? ctas : 1);
+    if (d.per_sample_weights != nullptr || d.pooling_mode == B200TBE_POOL_MEAN) {
+      reduce_runs_groups_kernel<KeyT, WT, GT, true, 4><<<run_grid, kRunThreads, 0, stream>>>(d);
+    } else {
+      reduce_runs_groups_kernel<KeyT, WT, GT, false, 4><<<run_grid, kRunThreads, 0, stream>>>(d);
+    }
+  } else {
+    stream_kernel<<<kNumSMs, kStreamThreads, kStreamSmemBytes, stream>>>(d);
+  }
   auto chunk_kernel = reduce_chunks_stream_kernel<KeyT, WT, GT, kVPL>;
   if (cudaFuncSetAttribute(chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(kStreamSmemBytes)) != cudaSuccess)

@@ -438,20 +438,33 @@ __device__ __forceinline__ bool stream_unit(const StreamBags& bags, const Stream
         }
         dst += 512;
       }
-    } else if (chunk_shift >= 0) {
-      // chunks per row is a power of two: a lane keeps its chunk and moves rows_per_it rows a step
-      const int rows_per_it = 32 >> chunk_shift;
-      const char* lane_base = tab.base + ((lane & ((1 << chunk_shift) - 1)) << 4);
-      int row = lane >> chunk_shift;
-      for (int it = 0; it < copy_iters; ++it) {
-        const uint32_t c = __shfl_sync(kFullMask, my_chunk, row);
-        if (c != 0xffffffffu)
-          asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst),
-                       "l"(lane_base + (static_cast<uint64_t>(c) << 4))
+    } else if (chunk_shift >= 1) {
+      // chunks per row is a power of two (at least 2): a lane copies a pair of adjacent chunks, so
+      // one shuffle and one address serve 32 bytes; 64 / chunks rows move per instruction pair
+      const int pair_shift = chunk_shift - 1;
+      const int rows_per_it = 32 >> pair_shift;
+      const char* lane_base = tab.base + ((lane & ((1 << pair_shift) - 1)) << 5);
+      uint32_t dst2 = smem_u32(ring.rows[slot]) + (lane << 5);
+      const int iters2 = (copy_iters + 1) >> 1;
+      int row = lane >> pair_shift;
+      for (int it = 0; it < iters2; ++it) {
+        const uint32_t c = __shfl_sync(kFullMask, my_chunk, row & 31);
+        if (row < rows_per_stage && c != 0xffffffffu) {
+          const char* src = lane_base + (static_cast<uint64_t>(c) << 4);
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst2), "l"(src) : "memory");
+          asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst2 + 16), "l"(src + 16)
                        : "memory");
+        }
         row += rows_per_it;
-        dst += 512;
+        dst2 += 1024;
       }
+    } else if (chunk_shift == 0) {
+      // 16-byte rows: one chunk per lane
+      const uint32_t c = my_chunk;
+      if (c != 0xffffffffu)
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst),
+                     "l"(tab.base + (static_cast<uint64_t>(c) << 4))
+                     : "memory");
     } else {
       int row = lane_row0, chunk = lane_chunk0;
       for (int it = 0; it < copy_iters; ++it) {
