@@ -767,28 +767,31 @@ int persistent_grid() {
 template <typename KeyT, typename WT, typename GT, int kVPL>
 int run_reduce(const BwdDev& d, cudaStream_t stream) {
   const int grid = persistent_grid();
-  auto stream_kernel = reduce_runs_stream_kernel<KeyT, WT, GT, kVPL>;
-  if (cudaFuncSetAttribute(stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           static_cast<int>(kStreamSmemBytes)) != cudaSuccess)
-    return B200TBE_ERR_LAUNCH;
   if (d.max_D <= 512) {
     // one warp per 32 runs; the run count is known on the device only, num_indices bounds it
     const int64_t ctas = (d.num_indices + 32 * kRunWarps - 1) / (32 * kRunWarps);
     if (ctas > 0x7fffffff) return B200TBE_ERR_TOO_LARGE;
     const unsigned run_grid = static_cast<unsigned>(ctas > 0 ? ctas : 1);
+    const int chunk_grid = kNumSMs * kRunCtasPerSm;
     if (d.per_sample_weights != nullptr || d.pooling_mode == B200TBE_POOL_MEAN) {
       reduce_runs_groups_kernel<KeyT, WT, GT, true, 4><<<run_grid, kRunThreads, 0, stream>>>(d);
+      reduce_chunks_groups_kernel<KeyT, GT, true, 4><<<chunk_grid, kRunThreads, 0, stream>>>(d);
     } else {
       reduce_runs_groups_kernel<KeyT, WT, GT, false, 4><<<run_grid, kRunThreads, 0, stream>>>(d);
+      reduce_chunks_groups_kernel<KeyT, GT, false, 4><<<chunk_grid, kRunThreads, 0, stream>>>(d);
     }
   } else {
+    auto stream_kernel = reduce_runs_stream_kernel<KeyT, WT, GT, kVPL>;
+    if (cudaFuncSetAttribute(stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(kStreamSmemBytes)) != cudaSuccess)
+      return B200TBE_ERR_LAUNCH;
     stream_kernel<<<kNumSMs, kStreamThreads, kStreamSmemBytes, stream>>>(d);
+    auto chunk_kernel = reduce_chunks_stream_kernel<KeyT, WT, GT, kVPL>;
+    if (cudaFuncSetAttribute(chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             static_cast<int>(kStreamSmemBytes)) != cudaSuccess)
+      return B200TBE_ERR_LAUNCH;
+    chunk_kernel<<<kNumSMs, kStreamThreads, kStreamSmemBytes, stream>>>(d);
   }
-  auto chunk_kernel = reduce_chunks_stream_kernel<KeyT, WT, GT, kVPL>;
-  if (cudaFuncSetAttribute(chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                           static_cast<int>(kStreamSmemBytes)) != cudaSuccess)
-    return B200TBE_ERR_LAUNCH;
-  chunk_kernel<<<kNumSMs, kStreamThreads, kStreamSmemBytes, stream>>>(d);
   finish_long_runs_kernel<KeyT, WT, GT, kVPL><<<grid, kBwdThreads, 0, stream>>>(d);
   return launch_status();
 }

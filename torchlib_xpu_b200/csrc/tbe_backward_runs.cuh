@@ -124,6 +124,34 @@ __device__ __forceinline__ void add_slice(float4 (&acc)[kQ], const bool (&on)[kQ
   }
 }
 
+// Whole warp on one run: group h sums lookups h, h + G, ... of the run and the groups' sums are
+// added by shuffle, so every lane ends with the run's complete sum of its quads.
+template <typename GT, bool kScaled, int kQ>
+__device__ __forceinline__ void sum_whole_warp(const BwdDev& p, const RunView& run, float4 (&acc)[kQ],
+                                               const bool (&on)[kQ], int64_t gstride_bytes, int lane,
+                                               int h, int G, int gs, int quad_g) {
+  for (uint32_t base = 0; base < run.len; base += 32) {
+    float mult;
+    const uint32_t goff = slice_of<kScaled>(p, run, base + lane, gstride_bytes, mult);
+    const int n = run.len - base < 32u ? static_cast<int>(run.len - base) : 32;
+    for (int j = h; j - h < n; j += G) {   // j - h is the same in every lane: the shuffles stay converged
+      const uint32_t ch = __shfl_sync(kFullMask, goff, j & 31);
+      float m = 1.f;
+      if (kScaled) m = __shfl_sync(kFullMask, mult, j & 31);
+      add_slice<GT, kScaled, kQ>(acc, on, run.g_lane, j < n ? ch : kNoSlice, m, quad_g);
+    }
+  }
+  for (int o = gs; o < 32; o <<= 1) {
+#pragma unroll
+    for (int k = 0; k < kQ; ++k) {
+      acc[k].x += __shfl_xor_sync(kFullMask, acc[k].x, o);
+      acc[k].y += __shfl_xor_sync(kFullMask, acc[k].y, o);
+      acc[k].z += __shfl_xor_sync(kFullMask, acc[k].z, o);
+      acc[k].w += __shfl_xor_sync(kFullMask, acc[k].w, o);
+    }
+  }
+}
+
 // The optimizer step for the run summed in acc (complete in every lane of the group). Every lane
 // runs this; only lanes with write set store.
 template <typename WT, int kQ>
@@ -228,6 +256,10 @@ __global__ void __launch_bounds__(kRunThreads, kQ <= 2 ? 8 : kRunCtasPerSm)
       mine.len = 0;
     } else {
       my_medium = mine.len > static_cast<uint32_t>(kShortRun);
+      // all 32 rows of the warp start their way from HBM now; the groups reach them a few steps later
+      for (int off = 0; off < D * static_cast<int>(sizeof(WT)); off += 128)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(mine.w_lane + off));
+      if (mine.mptr != nullptr) asm volatile("prefetch.global.L2 [%0];" ::"l"(mine.mptr));
     }
   }
   uint32_t medium = __ballot_sync(kFullMask, my_medium);
@@ -299,26 +331,63 @@ __global__ void __launch_bounds__(kRunThreads, kQ <= 2 ? 8 : kRunCtasPerSm)
     float4 acc[kQ];
 #pragma unroll
     for (int k = 0; k < kQ; ++k) acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
-    for (uint32_t base = 0; base < run.len; base += 32) {
-      float mult;
-      const uint32_t goff = slice_of<kScaled>(p, run, base + lane, gstride_bytes, mult);
-      const int n = run.len - base < 32u ? static_cast<int>(run.len - base) : 32;
-      for (int j = h; j - h < n; j += G) {   // j - h is the same in every lane: the shuffles stay converged
-        const uint32_t ch = __shfl_sync(kFullMask, goff, j & 31);
-        float m = 1.f;
-        if (kScaled) m = __shfl_sync(kFullMask, mult, j & 31);
-        add_slice<GT, kScaled, kQ>(acc, on, run.g_lane, j < n ? ch : kNoSlice, m, quad_g);
-      }
-    }
-    for (int o = gs; o < 32; o <<= 1) {
-#pragma unroll
-      for (int k = 0; k < kQ; ++k) {
-        acc[k].x += __shfl_xor_sync(kFullMask, acc[k].x, o);
-        acc[k].y += __shfl_xor_sync(kFullMask, acc[k].y, o);
-        acc[k].z += __shfl_xor_sync(kFullMask, acc[k].z, o);
-        acc[k].w += __shfl_xor_sync(kFullMask, acc[k].w, o);
-      }
-    }
+    sum_whole_warp<GT, kScaled, kQ>(p, run, acc, on, gstride_bytes, lane, h, G, gs, quad_g);
     update_row<WT, kQ>(p, run, acc, wv, on, m_old, h == 0, v, gs, quad_w);
+  }
+}
+
+// One warp per chunk of a long run (kLongRun lookups): the chunk's sum goes to its row of partials.
+template <typename KeyT, typename GT, bool kScaled, int kQ>
+__global__ void __launch_bounds__(kRunThreads, kRunCtasPerSm)
+    reduce_chunks_groups_kernel(const __grid_constant__ BwdDev p) {
+  const int lane = threadIdx.x & 31;
+  const int gs = lanes_per_row((p.max_D + 4 * kQ - 1) / (4 * kQ));
+  const int gshift = __ffs(gs) - 1;
+  const int G = 32 >> gshift;
+  const int h = lane >> gshift;
+  const int v = lane & (gs - 1);
+  const int64_t gstride_bytes = p.grad_stride * static_cast<int64_t>(sizeof(GT));
+  const int quad_g = gs * 4 * static_cast<int>(sizeof(GT));
+  const int64_t chunks = p.counters[2];
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * kRunWarps;
+  for (int64_t c = static_cast<int64_t>(blockIdx.x) * kRunWarps + (threadIdx.x >> 5); c < chunks; c += stride) {
+    const uint32_t slot = p.chunk_run[c];
+    const uint32_t long_id = p.long_run[slot];
+    const uint32_t s_run = p.run_start[long_id], e_run = p.run_start[long_id + 1];
+    const uint32_t s = s_run + static_cast<uint32_t>(c - p.long_chunk0[slot]) * kLongRun;
+    const uint32_t e = s + kLongRun < e_run ? s + kLongRun : e_run;
+    const int64_t key = static_cast<int64_t>(reinterpret_cast<const KeyT*>(p.sorted_keys)[s_run]);
+    int lo = 0, hi = p.T - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (__ldg(p.hash_size_cumsum + mid) <= key) {
+        lo = mid;
+      } else {
+        hi = mid - 1;
+      }
+    }
+    const int D_begin = __ldg(p.D_offsets + lo);
+    RunView run;
+    run.len = e - s;
+    run.start = s;
+    run.pay0 = p.sorted_vals[s];
+    run.bag0 = static_cast<uint32_t>(lo) * static_cast<uint32_t>(p.B);
+    run.D = __ldg(p.D_offsets + lo + 1) - D_begin;
+    run.w_lane = nullptr;
+    run.mptr = nullptr;
+    run.g_lane = p.grad_output + (p.grad_col_offset + D_begin) * static_cast<int64_t>(sizeof(GT)) +
+                 v * 4 * static_cast<int>(sizeof(GT));
+    bool on[kQ];
+    float4 acc[kQ];
+#pragma unroll
+    for (int k = 0; k < kQ; ++k) {
+      on[k] = (v + gs * k) * 4 < run.D;
+      acc[k] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    sum_whole_warp<GT, kScaled, kQ>(p, run, acc, on, gstride_bytes, lane, h, G, gs, quad_g);
+    float* dst = p.partials + c * p.max_D;
+#pragma unroll
+    for (int k = 0; k < kQ; ++k)
+      if (h == 0 && on[k]) *reinterpret_cast<float4*>(dst + (v + gs * k) * 4) = acc[k];
   }
 }
