@@ -1,18 +1,10 @@
 // TBE pooled forward over fp32 / fp16 tables.
 //
-// Rows of up to 512 bytes (every D <= 128 fp32 / D <= 256 fp16): one warp per bag, launched as a
-// plain grid of bags with few registers per thread, so that ~48 warps are resident per SM and the
-// hardware's CTA scheduling balances the load. Measured on B200 this simple shape beats both a
-// persistent software-pipelined variant and the shared-memory ring engine (which stops at ~19 G
-// rows/s for 256-byte rows): a random-row read kernel reaches 28 G rows/s out of HBM and 51 G
-// rows/s out of L2 only at high occupancy. A row of C 16-byte vectors is fetched by a group of gs
-// lanes (C rounded up to a power of two), so one load instruction brings 32/gs rows (two 256-byte
-// rows); the bag's ids are read 32 at a time with one coalesced load and handed out by shuffle as
-// 32-bit chunk numbers; loads allocate in L1, where the hottest rows of a skewed id stream hit;
-// fp16 elements are added to fp32 accumulators with the mixed-precision add of sm_100.
-// Wider rows run on the ring engine of tbe_stream.cuh; rows that are not whole aligned 16-byte
+// Rows of up to 512 bytes (every D <= 128 fp32 / D <= 256 fp16): one warp per bag on the register
+// gather of tbe_bags.cuh, a plain grid at 64 warps per SM. Wider rows run on the shared-memory ring
+// engine of tbe_stream.cuh (persistent, one CTA per SM); rows that are not whole aligned 16-byte
 // vectors on a scalar path.
-#include "tbe_stream.cuh"
+#include "tbe_bags.cuh"
 
 namespace b200tbe {
 namespace {
@@ -80,76 +72,9 @@ __global__ void __launch_bounds__(kStreamThreads, 1)
   }
 }
 
-// ---- one warp per bag, rows of at most 512 bytes ---------------------------------------------
-constexpr int kBagWarps = 8;
-constexpr int kBagThreads = kBagWarps * 32;
-constexpr int kBagCtasPerSm = 8;   // 64 warps per SM, 32 registers per thread: measured best (5: +20 %, 6: +21 %)
-constexpr int kBagLoads = 2;       // 16-byte loads in flight per lane
-constexpr uint32_t kNoRow = 0xffffffffu;
-
-__device__ __forceinline__ uint4 ldg_cached16(const void* p) {
-  uint4 v;
-  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "l"(p));
-  return v;
-}
-
-// acc[0..1] += the two fp16 halves of one 32-bit word, one mixed-precision add each.
-__device__ __forceinline__ void add_half2(float& a0, float& a1, uint32_t h2) {
-  asm("{.reg .f16 l, h;\n"
-      "mov.b32 {l, h}, %2;\n"
-      "add.rn.f32.f16 %0, l, %0;\n"
-      "add.rn.f32.f16 %1, h, %1;}\n"
-      : "+f"(a0), "+f"(a1)
-      : "r"(h2));
-}
-
-template <typename WT>
-struct Vec16;
-template <>
-struct Vec16<float> {
-  static constexpr int kE = 4;
-  static __device__ __forceinline__ void add(float (&a)[4], uint4 x) {
-    a[0] += __uint_as_float(x.x);
-    a[1] += __uint_as_float(x.y);
-    a[2] += __uint_as_float(x.z);
-    a[3] += __uint_as_float(x.w);
-  }
-  static __device__ __forceinline__ void fma(float (&a)[4], uint4 x, float w) {
-    a[0] = fmaf(__uint_as_float(x.x), w, a[0]);
-    a[1] = fmaf(__uint_as_float(x.y), w, a[1]);
-    a[2] = fmaf(__uint_as_float(x.z), w, a[2]);
-    a[3] = fmaf(__uint_as_float(x.w), w, a[3]);
-  }
-};
-template <>
-struct Vec16<__half> {
-  static constexpr int kE = 8;
-  static __device__ __forceinline__ void add(float (&a)[8], uint4 x) {
-    add_half2(a[0], a[1], x.x);
-    add_half2(a[2], a[3], x.y);
-    add_half2(a[4], a[5], x.z);
-    add_half2(a[6], a[7], x.w);
-  }
-  static __device__ __forceinline__ void fma(float (&a)[8], uint4 x, float w) {
-    const float2 p0 = half2_bits_to_float2(x.x), p1 = half2_bits_to_float2(x.y),
-                 p2 = half2_bits_to_float2(x.z), p3 = half2_bits_to_float2(x.w);
-    a[0] = fmaf(p0.x, w, a[0]);
-    a[1] = fmaf(p0.y, w, a[1]);
-    a[2] = fmaf(p1.x, w, a[2]);
-    a[3] = fmaf(p1.y, w, a[3]);
-    a[4] = fmaf(p2.x, w, a[4]);
-    a[5] = fmaf(p2.y, w, a[5]);
-    a[6] = fmaf(p3.x, w, a[6]);
-    a[7] = fmaf(p3.y, w, a[7]);
-  }
-};
-
 template <typename WT, typename OT, typename IndexT, bool kWeighted>
 __global__ void __launch_bounds__(kBagThreads, kBagCtasPerSm)
     tbe_forward_bags_kernel(const __grid_constant__ FwdParams p) {
-  constexpr int kE = Vec16<WT>::kE;
   const int lane = threadIdx.x & 31;
   const int64_t bag = static_cast<int64_t>(blockIdx.x) * kBagWarps + (threadIdx.x >> 5);
   if (bag >= static_cast<int64_t>(p.T) * p.B) return;
@@ -169,77 +94,10 @@ __global__ void __launch_bounds__(kBagThreads, kBagCtasPerSm)
                                   p.output_col_offset + D_begin, p.rows_per_dest, bag, b, 1, lane);
     return;
   }
-  const int64_t start = load_index<IndexT>(p.offsets, bag);
-  const int64_t end = load_index<IndexT>(p.offsets, bag + 1);
-  const int len = end - start > 0x7fffffff ? 0x7fffffff : static_cast<int>(end - start);
-  const IndexT* idx = reinterpret_cast<const IndexT*>(p.indices) + start;
-  const float* psw = kWeighted ? p.per_sample_weights + start : nullptr;
-  const int vecs = row_bytes >> 4;
-  const int gs = lanes_per_row(vecs);
-  const int gshift = __ffs(gs) - 1;
-  const int G = 32 >> gshift;            // rows per load instruction
-  const int h = lane >> gshift;          // this lane's group
-  const int v = lane & (gs - 1);         // this lane's vector inside the row
-  const bool active = v < vecs;
-  const char* lane_base = table + (v << 4);
-
-  float acc[kE];
-#pragma unroll
-  for (int e = 0; e < kE; ++e) acc[e] = 0.f;
-
-  for (int c = 0; c < len; c += 32) {
-    const int n = len - c < 32 ? len - c : 32;
-    // this lane's row id; ids do not fit 32 bits only in tables no memory holds
-    uint32_t my_row = kNoRow;
-    float my_w = 1.f;
-    if (lane < n) {
-      const int64_t i = static_cast<int64_t>(__ldg(idx + c + lane));
-      if (kWeighted) my_w = __ldg(psw + c + lane);
-      if (i < 0 || i >= (num_rows >= 0 ? num_rows : int64_t{0xffffffff})) {
-        if (p.status != nullptr) atomicOr(p.status, B200TBE_DEV_INDEX_OUT_OF_RANGE);
-      } else {
-        my_row = static_cast<uint32_t>(i);
-      }
-    }
-    for (int j = 0; j < n; j += G * kBagLoads) {
-      uint4 x[kBagLoads];
-      float w[kBagLoads];
-#pragma unroll
-      for (int u = 0; u < kBagLoads; ++u) {
-        const int rr = j + u * G + h;
-        const uint32_t row = __shfl_sync(kFullMask, my_row, rr & 31);
-        if (kWeighted) w[u] = __shfl_sync(kFullMask, my_w, rr & 31);
-        x[u] = make_uint4(0u, 0u, 0u, 0u);  // +0.0 in either type: adding it changes nothing
-        if (rr < n && row != kNoRow && active)
-          x[u] = ldg_cached16(lane_base + static_cast<uint64_t>(row) * static_cast<uint32_t>(row_bytes));
-      }
-#pragma unroll
-      for (int u = 0; u < kBagLoads; ++u) {
-        if (kWeighted) {
-          Vec16<WT>::fma(acc, x[u], w[u]);
-        } else {
-          Vec16<WT>::add(acc, x[u]);
-        }
-      }
-    }
-  }
-  for (int o = gs; o < 32; o <<= 1) {
-#pragma unroll
-    for (int e = 0; e < kE; ++e) acc[e] += __shfl_xor_sync(kFullMask, acc[e], o);
-  }
-  if (h == 0 && active) {
-    const float scale =
-        (p.pooling_mode == B200TBE_POOL_MEAN && len > 0) ? 1.f / static_cast<float>(len) : 1.f;
-    const int rpd = static_cast<int>(p.rows_per_dest);
-    const int dest = b / rpd;
-    OT* dst = outputs[dest] + static_cast<int64_t>(b - dest * rpd) * p.output_stride +
-              p.output_col_offset + D_begin + v * kE;
-    float r[kE];
-#pragma unroll
-    for (int e = 0; e < kE; ++e) r[e] = acc[e] * scale;
-#pragma unroll
-    for (int e = 0; e < kE; e += 4) store_pooled<OT, 4>(dst + e, r + e);
-  }
+  const BagLaunch<OT> launch{p.indices, p.offsets, p.per_sample_weights, p.status, p.pooling_mode,
+                             outputs, p.output_stride, p.rows_per_dest};
+  pool_float_bag<WT, OT, IndexT, kWeighted>(launch, table, row_bytes, num_rows,
+                                            p.output_col_offset + D_begin, bag, b, lane);
 }
 
 template <typename WT, typename OT, typename IndexT>
