@@ -99,6 +99,8 @@ __device__ __forceinline__ void pool_float_bag(const BagLaunch<OT>& p, const cha
                                                int64_t num_rows, int64_t col, int64_t bag, int b,
                                                int lane) {
   constexpr int kE = Vec16<WT>::kE;
+  // fp32 rows leave registers for more loads in flight: 4 accumulators per lane instead of 8
+  constexpr int kLoads = sizeof(WT) == 4 ? 2 * kBagLoads : kBagLoads;
   const int64_t start = load_index<IndexT>(p.offsets, bag);
   const int64_t end = load_index<IndexT>(p.offsets, bag + 1);
   const int len = end - start > 0x7fffffff ? 0x7fffffff : static_cast<int>(end - start);
@@ -131,11 +133,11 @@ __device__ __forceinline__ void pool_float_bag(const BagLaunch<OT>& p, const cha
         my_row = static_cast<uint32_t>(i);
       }
     }
-    for (int j = 0; j < n; j += G * kBagLoads) {
-      uint4 x[kBagLoads];
-      float w[kBagLoads];
+    for (int j = 0; j < n; j += G * kLoads) {
+      uint4 x[kLoads];
+      float w[kLoads];
 #pragma unroll
-      for (int u = 0; u < kBagLoads; ++u) {
+      for (int u = 0; u < kLoads; ++u) {
         const int rr = j + u * G + h;
         const uint32_t row = __shfl_sync(kFullMask, my_row, rr & 31);
         if (kWeighted) w[u] = __shfl_sync(kFullMask, my_w, rr & 31);
@@ -144,7 +146,7 @@ __device__ __forceinline__ void pool_float_bag(const BagLaunch<OT>& p, const cha
           x[u] = ldg_cached16(lane_base + static_cast<uint64_t>(row) * static_cast<uint32_t>(row_bytes));
       }
 #pragma unroll
-      for (int u = 0; u < kBagLoads; ++u) {
+      for (int u = 0; u < kLoads; ++u) {
         if (kWeighted) {
           Vec16<WT>::fma(acc, x[u], w[u]);
         } else {

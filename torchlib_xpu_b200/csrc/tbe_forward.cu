@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1)
 }
 
 template <typename WT, typename OT, typename IndexT, bool kWeighted>
-__global__ void __launch_bounds__(kBagThreads, kBagCtasPerSm)
+__global__ void __launch_bounds__(kBagThreads, sizeof(WT) == 4 ? kBagCtasPerSm - 2 : kBagCtasPerSm)
     tbe_forward_bags_kernel(const __grid_constant__ FwdParams p) {
   const int lane = threadIdx.x & 31;
   const int64_t bag = static_cast<int64_t>(blockIdx.x) * kBagWarps + (threadIdx.x >> 5);
