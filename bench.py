@@ -127,8 +127,10 @@ def backward_launches(bits: int) -> int:
 
 def time_launches(fn, iters, flush=None):
     """Median and mean device time (ms) of fn() over iters launches, one CUDA-event pair each, with an
-    optional L2 flush between launches (outside the timed pairs)."""
+    optional L2 flush between launches (outside the timed pairs), after 3 untimed launches."""
     times = []
+    for _ in range(3):
+        fn()
     for _ in range(iters):
         if flush is not None:
             flush.zero_()

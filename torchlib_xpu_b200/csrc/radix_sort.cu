@@ -51,12 +51,16 @@ __global__ void __launch_bounds__(kSortThreads)
 
 // Shared memory of the scatter kernel: per-warp digit counters (16 bits are enough: a warp holds
 // at most 32 * kItems keys, a tile at most 4096), the tile-level digit offsets, and the staging
-// area in which the tile is reordered. 56 KB for 4-byte keys: four CTAs per SM.
+// area in which the tile is reordered. Once the tile is staged the counters are dead and their
+// space holds the per-digit distance from staging position to global position. 52 KB for 4-byte
+// keys: four CTAs per SM.
 template <typename KeyT>
 struct ScatterSmem {
-  uint16_t warp_hist[kSortWarps][kMaxRadix];
+  union {
+    uint16_t warp_hist[kSortWarps][kMaxRadix];
+    uint32_t delta[kMaxRadix];
+  };
   uint32_t digit_start[kMaxRadix];
-  uint32_t delta[kMaxRadix];
   KeyT keys[SortTile<KeyT>::kTile];
   uint32_t vals[SortTile<KeyT>::kTile];
 };
@@ -122,7 +126,7 @@ __global__ void __launch_bounds__(kSortThreads, 4)
 
   // per digit: exclusive prefix over the warps, then over the digits of the tile; thread i owns
   // the kDigitsPerThread consecutive digits starting at i * kDigitsPerThread
-  uint32_t totals[kDigitsPerThread];
+  uint32_t totals[kDigitsPerThread], run_total[kDigitsPerThread];
   uint32_t thread_total = 0;
 #pragma unroll
   for (int j = 0; j < kDigitsPerThread; ++j) {
@@ -134,7 +138,7 @@ __global__ void __launch_bounds__(kSortThreads, 4)
       sm.warp_hist[w][d] = static_cast<uint16_t>(run);
       run += c;
     }
-    totals[j] = run;
+    run_total[j] = run;
     thread_total += run;
   }
   uint32_t unused_total;
@@ -143,8 +147,9 @@ __global__ void __launch_bounds__(kSortThreads, 4)
   for (int j = 0; j < kDigitsPerThread; ++j) {
     const int d = threadIdx.x * kDigitsPerThread + j;
     sm.digit_start[d] = start;
-    if (d < radix) sm.delta[d] = positions[static_cast<int64_t>(d) * num_tiles + blockIdx.x] - start;
-    start += totals[j];
+    // global position of the tile's first key of digit d, minus its staging position
+    totals[j] = (d < radix ? positions[static_cast<int64_t>(d) * num_tiles + blockIdx.x] : 0u) - start;
+    start += run_total[j];
   }
   __syncthreads();
 
@@ -158,6 +163,9 @@ __global__ void __launch_bounds__(kSortThreads, 4)
       sm.vals[pos] = vals_in[base + it];
     }
   }
+  __syncthreads();
+#pragma unroll
+  for (int j = 0; j < kDigitsPerThread; ++j) sm.delta[threadIdx.x * kDigitsPerThread + j] = totals[j];
   __syncthreads();
 
   for (int i = threadIdx.x; i < tile_n; i += kSortThreads) {

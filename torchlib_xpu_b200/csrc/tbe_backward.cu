@@ -66,28 +66,52 @@ struct BwdDev {
 };
 
 // ---- linearize -----------------------------------------------------------------------------
+// One warp per 32 consecutive bags: lane i holds the start of bag i (relative to the group's first
+// lookup) and the bag's table; the group's lookups are then walked 32 at a time, fully coalesced,
+// and each lookup finds its bag with a 5-step search over the lanes' starts.
 template <typename KeyT, typename IndexT, bool kWeighted>
 __global__ void __launch_bounds__(kBwdThreads)
     linearize_kernel(BwdDev p, KeyT* __restrict__ keys, uint32_t* __restrict__ vals) {
   const int lane = threadIdx.x & 31;
-  const int64_t bag = static_cast<int64_t>(blockIdx.x) * kBwdWarps + (threadIdx.x >> 5);
-  if (bag >= static_cast<int64_t>(p.T) * p.B) return;
-  const int t = static_cast<int>(bag / p.B);
-  const int64_t h0 = __ldg(p.hash_size_cumsum + t);
-  const int64_t rows = __ldg(p.hash_size_cumsum + t + 1) - h0;
-  const int64_t start = load_index<IndexT>(p.offsets, bag);
-  const int64_t end = load_index<IndexT>(p.offsets, bag + 1);
-  for (int64_t j = start + lane; j < end; j += 32) {
-    int64_t idx = load_index<IndexT>(p.indices, j);
-    uint32_t payload = kWeighted ? static_cast<uint32_t>(j) : static_cast<uint32_t>(bag);
-    if (idx < 0 || idx >= rows) {
-      if (p.status != nullptr) atomicOr(p.status, B200TBE_DEV_INDEX_OUT_OF_RANGE);
-      idx = 0;
-      payload = kInvalidPayload;
+  const int64_t total_bags = static_cast<int64_t>(p.T) * p.B;
+  const int64_t bag0 = (static_cast<int64_t>(blockIdx.x) * kBwdWarps + (threadIdx.x >> 5)) * 32;
+  if (bag0 >= total_bags) return;
+  const int nb = total_bags - bag0 < 32 ? static_cast<int>(total_bags - bag0) : 32;
+  const int64_t begin = load_index<IndexT>(p.offsets, bag0);
+  const int64_t end = load_index<IndexT>(p.offsets, bag0 + nb);
+  const int64_t mine = load_index<IndexT>(p.offsets, bag0 + (lane < nb ? lane : nb));
+  // a group of 32 bags longer than 2^32 lookups does not occur in memory that exists
+  const uint32_t my_start = static_cast<uint32_t>(mine - begin);
+  const int my_t = static_cast<int>((bag0 + (lane < nb ? lane : nb - 1)) / p.B);
+  const int64_t my_h0 = __ldg(p.hash_size_cumsum + my_t);
+  const int64_t my_rows = __ldg(p.hash_size_cumsum + my_t + 1) - my_h0;
+  const uint32_t total = static_cast<uint32_t>(end - begin);
+  for (uint32_t base = 0; base < total; base += 32) {
+    const uint32_t rel = base + lane;
+    // the last bag whose start is <= rel (empty bags share a start with their successor)
+    int b = 0;
+#pragma unroll
+    for (int step = 16; step > 0; step >>= 1) {
+      const int cand = b + step;
+      const uint32_t s = __shfl_sync(kFullMask, my_start, cand & 31);
+      if (cand < nb && s <= rel) b = cand;
     }
-    keys[j] = static_cast<KeyT>(h0 + idx);
-    vals[j] = payload;
-    if (kWeighted) p.bag_of_pos[j] = static_cast<uint32_t>(bag);
+    const int64_t h0 = __shfl_sync(kFullMask, my_h0, b);
+    const int64_t rows = __shfl_sync(kFullMask, my_rows, b);
+    if (rel < total) {
+      const int64_t j = begin + rel;
+      int64_t idx = load_index<IndexT>(p.indices, j);
+      const uint32_t bag = static_cast<uint32_t>(bag0 + b);
+      uint32_t payload = kWeighted ? static_cast<uint32_t>(j) : bag;
+      if (idx < 0 || idx >= rows) {
+        if (p.status != nullptr) atomicOr(p.status, B200TBE_DEV_INDEX_OUT_OF_RANGE);
+        idx = 0;
+        payload = kInvalidPayload;
+      }
+      keys[j] = static_cast<KeyT>(h0 + idx);
+      vals[j] = payload;
+      if (kWeighted) p.bag_of_pos[j] = bag;
+    }
   }
 }
 
@@ -818,7 +842,7 @@ int run_backward(BwdDev d, const b200tbe_backward_params* p, const ScratchLayout
 
   if (cudaMemsetAsync(d.counters, 0, 256, stream) != cudaSuccess) return B200TBE_ERR_LAUNCH;
   const int64_t bags = static_cast<int64_t>(p->T) * p->B;
-  const int64_t lin_ctas = (bags + kBwdWarps - 1) / kBwdWarps;
+  const int64_t lin_ctas = (bags + 32 * kBwdWarps - 1) / (32 * kBwdWarps);
   if (lin_ctas > 0x7fffffff) return B200TBE_ERR_TOO_LARGE;
   if (weighted) {
     linearize_kernel<KeyT, IndexT, true>
