@@ -796,7 +796,7 @@ int run_reduce(const BwdDev& d, cudaStream_t stream) {
     const int64_t ctas = (d.num_indices + 32 * kRunWarps - 1) / (32 * kRunWarps);
     if (ctas > 0x7fffffff) return B200TBE_ERR_TOO_LARGE;
     const unsigned run_grid = static_cast<unsigned>(ctas > 0 ? ctas : 1);
-    const int chunk_grid = kNumSMs * kRunCtasPerSm;
+    const int chunk_grid = kNumSMs * run_ctas_per_sm<GT>();
     if (d.per_sample_weights != nullptr || d.pooling_mode == B200TBE_POOL_MEAN) {
       reduce_runs_groups_kernel<KeyT, WT, GT, true, 4><<<run_grid, kRunThreads, 0, stream>>>(d);
       reduce_chunks_groups_kernel<KeyT, GT, true, 4><<<chunk_grid, kRunThreads, 0, stream>>>(d);
