@@ -245,6 +245,22 @@ B200TBE_API int b200tbe_dequantize_rows(const uint8_t* src, int64_t rows, int32_
                                         int32_t dst_dtype, b200tbe_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * NV12 -> packed RGB24, BT.709: replaces the reference plugin's only device kernel,
+ * convertNV12ToRGB(queue, y_plane, uv_plane, rgb_output, width, height, stride, fullrange)
+ * (packages/torchcodec-xpu/src/torchcodec_xpu/ColorConversionKernel.h:12-20, .cpp:160-181), called
+ * from XpuDeviceInterface.cpp:448-456 on the decoded VAAPI surface with fullrange = false. Same argument meaning; the
+ * stream replaces the SYCL queue and, unlike the reference (a blocking queue.wait()), the call does
+ * not synchronise. y_plane / uv_plane: device pointers to the luma plane and the interleaved U,V
+ * plane, `stride` bytes per row in both; rgb: [height, width, 3] bytes. tiled = 1 reads the Intel
+ * Tile-Y layout the reference's surfaces have (stride a multiple of 128, plane heights padded to 32
+ * rows); tiled = 0 reads linear-pitch planes (what a CUDA decoder produces). fullrange selects the
+ * reference's second normalisation, restated as written there (.cpp:84-88).
+ * ---------------------------------------------------------------------------------------------- */
+B200TBE_API int b200tbe_nv12_to_rgb(const uint8_t* y_plane, const uint8_t* uv_plane, uint8_t* rgb,
+                                    int32_t width, int32_t height, int32_t stride, int32_t fullrange,
+                                    int32_t tiled, b200tbe_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Gradient exchange of the table-wise-sharded configuration (the step a sharded caller runs between
  * its dense part and b200tbe_backward; the pooled rows travel the other way inside b200tbe_forward,
  * which can scatter into peer-mapped destination buffers). Source s is a peer's gradient matrix

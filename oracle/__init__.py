@@ -249,3 +249,41 @@ def jagged_dense_elementwise_add(x_values, offsets_list, y):
 
 def num_threads() -> int:
     return int(ref_lib().ref_num_threads())
+
+
+# ---- NV12 -> RGB24 (nv12_oracle.c) ----------------------------------------------------------
+_nv12 = None
+
+
+def nv12_lib():
+    global _nv12
+    if _nv12 is None:
+        _nv12 = ctypes.CDLL(_build.build_nv12_oracle())
+        _nv12.nv12_oracle_offset.restype = ctypes.c_size_t
+        _nv12.nv12_oracle_offset.argtypes = [ctypes.c_int] * 4
+        _nv12.nv12_oracle_pixel.restype = None
+        _nv12.nv12_oracle_pixel.argtypes = [ctypes.c_uint8] * 3 + [ctypes.c_int, ctypes.c_void_p]
+        _nv12.nv12_oracle_convert.restype = None
+        _nv12.nv12_oracle_convert.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int] * 5
+    return _nv12
+
+
+def nv12_offset(x: int, y: int, stride: int, tiled: bool) -> int:
+    return int(nv12_lib().nv12_oracle_offset(x, y, stride, int(tiled)))
+
+
+def nv12_pixel(y: int, u: int, v: int, fullrange: bool = False):
+    out = np.zeros(3, dtype=np.uint8)
+    nv12_lib().nv12_oracle_pixel(y, u, v, int(fullrange), _ptr(out))
+    return tuple(int(c) for c in out)
+
+
+def nv12_to_rgb(y_plane, uv_plane, width: int, height: int, stride: int, fullrange: bool = False,
+                tiled: bool = False):
+    """y_plane / uv_plane: contiguous uint8 arrays (surface bytes); returns [height, width, 3] uint8."""
+    y_plane = np.ascontiguousarray(y_plane, dtype=np.uint8)
+    uv_plane = np.ascontiguousarray(uv_plane, dtype=np.uint8)
+    rgb = np.empty((height, width, 3), dtype=np.uint8)
+    nv12_lib().nv12_oracle_convert(_ptr(y_plane), _ptr(uv_plane), _ptr(rgb), width, height, stride,
+                                   int(fullrange), int(tiled))
+    return rgb

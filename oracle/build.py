@@ -3,6 +3,8 @@
   oracle/_build/libtbe_oracle.so       plain-C restatement (tbe_oracle.c), OpenMP
   oracle/_build/libfbgemm_core_ref.so  harness around the FBGEMM-core kernels inside torch's
                                        libtorch_cpu.so (fbgemm_core_ref.cpp)
+  oracle/_build/libnv12_oracle.so      NV12 -> RGB24 colour conversion (nv12_oracle.c), built without
+                                       floating-point contraction
 
 Run as `python oracle/build.py`; __graft_entry__.build() calls build_all() too.
 """
@@ -39,6 +41,16 @@ def build_c_oracle(force: bool = False) -> str:
     return lib
 
 
+def build_nv12_oracle(force: bool = False) -> str:
+    os.makedirs(OUT, exist_ok=True)
+    src = os.path.join(HERE, "nv12_oracle.c")
+    lib = os.path.join(OUT, "libnv12_oracle.so")
+    if force or _stale(lib, [src]):
+        _run(["gcc", "-O2", "-ffp-contract=off", "-fPIC", "-shared", "-fvisibility=hidden", "-std=c11",
+              "-Wall", "-Wextra", "-o", lib, src])
+    return lib
+
+
 def build_fbgemm_core_ref(force: bool = False) -> str:
     import torch
 
@@ -56,7 +68,8 @@ def build_fbgemm_core_ref(force: bool = False) -> str:
 
 
 def build_all(force: bool = False) -> dict[str, str]:
-    return {"c_oracle": build_c_oracle(force), "fbgemm_core_ref": build_fbgemm_core_ref(force)}
+    return {"c_oracle": build_c_oracle(force), "fbgemm_core_ref": build_fbgemm_core_ref(force),
+            "nv12_oracle": build_nv12_oracle(force)}
 
 
 if __name__ == "__main__":

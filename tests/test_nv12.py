@@ -1,0 +1,84 @@
+"""NV12 -> RGB24 oracle (CPU): known answers of BT.709 and the Tile-Y address map.
+
+The reference holds no vectors for its colour-conversion kernel
+(packages/torchcodec-xpu/src/torchcodec_xpu/ColorConversionKernel.cpp); what pins the restatement
+is the standard itself: limited-range black / white / grey and the 100 % primaries, and for the tiled
+layout the properties the reference's address function has (a bijection of every 4 KB tile onto
+itself, 16-byte columns kept contiguous)."""
+import numpy as np
+import pytest
+
+import oracle
+
+
+@pytest.mark.parametrize("yuv,rgb", [
+    ((16, 128, 128), (0, 0, 0)),          # black
+    ((235, 128, 128), (255, 255, 255)),   # white
+    ((126, 128, 128), (128, 128, 128)),   # mid grey: (126 - 16) / 219 * 255 = 128.08
+    ((63, 102, 240), (255, 0, 0)),        # BT.709 red   (Y 62.7, Cb 102.4, Cr 240)
+    ((32, 240, 118), (0, 0, 255)),        # BT.709 blue  (Y 31.8, Cb 240, Cr 117.6)
+])
+def test_limited_range_known_answers(yuv, rgb):
+    got = oracle.nv12_pixel(*yuv)
+    assert all(abs(g - w) <= 1 for g, w in zip(got, rgb)), (got, rgb)
+
+
+def test_green_primary_and_clamping():
+    r, g, b = oracle.nv12_pixel(173, 42, 26)      # BT.709 green (Y 172.8, Cb 41.6, Cr 26.3)
+    assert r <= 1 and g == 255 and b <= 2
+    assert oracle.nv12_pixel(255, 128, 128) == (255, 255, 255)   # above nominal white: clamped, not wrapped
+    assert oracle.nv12_pixel(0, 128, 128) == (0, 0, 0)           # below nominal black: clamped at zero
+
+
+def test_full_range_formula_as_the_reference_writes_it():
+    # ColorConversionKernel.cpp:84-88: chroma is (c - 128) / 255 - 0.5, so neutral chroma 128 is NOT
+    # neutral in this mode; the restatement keeps that, digit for digit
+    y, u, v = 200, 128, 128
+    s0, s1, s2 = np.float32(y) / np.float32(255), np.float32(-0.5), np.float32(-0.5)
+    want = []
+    for m in ((1.0, 0.0, 1.5748), (1.0, -0.187324, -0.468124), (1.0, 1.8556, 0.0)):
+        d = np.float32(s0 * np.float32(m[0]))
+        d = np.float32(d + np.float32(s1 * np.float32(m[1])))
+        d = np.float32(d + np.float32(s2 * np.float32(m[2])))
+        want.append(int(min(max(np.float32(d * np.float32(255)), 0), 255)))
+    assert oracle.nv12_pixel(y, u, v, fullrange=True) == tuple(want)
+
+
+def test_tile_y_offsets_are_a_bijection_with_contiguous_16_byte_columns():
+    stride, rows = 384, 64
+    seen = np.zeros(stride * rows, dtype=np.int32)
+    for y in range(rows):
+        for x in range(stride):
+            seen[oracle.nv12_offset(x, y, stride, True)] += 1
+    assert np.all(seen == 1)
+    # a tile is 128 bytes x 32 rows = 4096 bytes and tiles follow each other row-major
+    assert oracle.nv12_offset(128, 0, stride, True) // 4096 == 1
+    assert oracle.nv12_offset(0, 32, stride, True) // 4096 == stride // 128
+    # 16 aligned bytes of a row stay together; the next row of the same column is 16 bytes on
+    for y in (0, 5, 31):
+        for x in (0, 16, 64, 112):
+            base = oracle.nv12_offset(x, y, stride, True)
+            assert [oracle.nv12_offset(x + i, y, stride, True) for i in range(16)] == list(range(base, base + 16))
+    assert oracle.nv12_offset(0, 1, stride, True) - oracle.nv12_offset(0, 0, stride, True) == 16
+    # the two 64-byte halves trade places in every second group of 4 rows
+    assert oracle.nv12_offset(0, 0, stride, True) == 0
+    # (without the swap column 4 of group 0 starts at byte 256 and column 0 of group 1 at byte 512)
+    assert oracle.nv12_offset(64, 0, stride, True) == 512 and oracle.nv12_offset(0, 4, stride, True) == 256
+    assert oracle.nv12_offset(64, 4, stride, True) == (1 * 8 + 4) * 64
+    # linear layout
+    assert oracle.nv12_offset(7, 3, stride, False) == 3 * stride + 7
+
+
+def test_frame_conversion_uses_one_chroma_sample_per_2x2_block():
+    w, h, stride = 6, 4, 8
+    yp = np.full((h, stride), 126, dtype=np.uint8)
+    uv = np.full((h // 2, stride), 128, dtype=np.uint8)
+    uv[1, 2:4] = (102, 240)      # chroma of the block at columns 2-3, rows 2-3: red-ish
+    rgb = oracle.nv12_to_rgb(yp, uv, w, h, stride)
+    assert rgb.shape == (h, w, 3)
+    grey = oracle.nv12_pixel(126, 128, 128)
+    red = oracle.nv12_pixel(126, 102, 240)
+    for y in range(h):
+        for x in range(w):
+            want = red if (y >= 2 and 2 <= x <= 3) else grey
+            assert tuple(int(c) for c in rgb[y, x]) == want

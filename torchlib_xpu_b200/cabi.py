@@ -90,7 +90,7 @@ EXPORTS = (
     "b200tbe_backward_scratch_bytes", "b200tbe_backward", "b200tbe_radix_sort_scratch_bytes",
     "b200tbe_radix_sort_pairs", "b200tbe_radix_sort_pairs_static_max",
     "b200tbe_radix_sort_pairs_static", "b200tbe_exchange_pull", "b200tbe_quantized_row_bytes",
-    "b200tbe_quantize_rows", "b200tbe_dequantize_rows", "b200tbe_jagged_to_padded_dense", "b200tbe_dense_to_jagged",
+    "b200tbe_quantize_rows", "b200tbe_dequantize_rows", "b200tbe_nv12_to_rgb", "b200tbe_jagged_to_padded_dense", "b200tbe_dense_to_jagged",
     "b200tbe_jagged_dense_elementwise_add",
 )
 
@@ -135,6 +135,7 @@ def lib() -> ctypes.CDLL:
         _lib.b200tbe_dequantize_rows.argtypes = [
             _c_void_p, ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,
             _c_void_p, ctypes.c_int32, _c_void_p]
+        _lib.b200tbe_nv12_to_rgb.argtypes = [_c_void_p, _c_void_p, _c_void_p] + [ctypes.c_int32] * 5 + [_c_void_p]
         _lib.b200tbe_forward.argtypes = [ctypes.POINTER(ForwardParams), _c_void_p]
         _lib.b200tbe_nbit_forward.argtypes = [ctypes.POINTER(NbitForwardParams), _c_void_p]
         _lib.b200tbe_backward.argtypes = [ctypes.POINTER(BackwardParams), _c_void_p]
@@ -308,6 +309,20 @@ def dequantize_rows(rows_u8, D, ty, row_alignment=16, header_first=True, dtype=t
     check(lib().b200tbe_dequantize_rows(_p(rows_u8), rows, D, ty, row_alignment, int(header_first),
                                         _p(out), _TORCH_TO_CODE[dtype], _stream()),
           "b200tbe_dequantize_rows")
+    return out
+
+
+def nv12_to_rgb(y_plane, uv_plane, width, height, stride, fullrange=False, tiled=False, out=None):
+    """NV12 surface (uint8 CUDA tensors holding the luma and the interleaved chroma plane, `stride`
+    bytes per row, linear pitch or Intel Tile-Y) -> [height, width, 3] uint8 RGB, BT.709
+    (b200tbe_nv12_to_rgb; the reference's convertNV12ToRGB)."""
+    if y_plane.dtype != torch.uint8 or uv_plane.dtype != torch.uint8:
+        raise B200TbeError("planes must be uint8")
+    if out is None:
+        out = torch.empty((height, width, 3), dtype=torch.uint8, device=y_plane.device)
+    check(lib().b200tbe_nv12_to_rgb(_p(y_plane), _p(uv_plane), _p(out), width, height, stride,
+                                    int(bool(fullrange)), int(bool(tiled)), _stream()),
+          "b200tbe_nv12_to_rgb")
     return out
 
 
