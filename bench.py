@@ -274,7 +274,7 @@ def reference_arm(args, cfg, rank, json_out):
 # The other named configurations, single GPU, one kernel (or kernel group) each
 # --------------------------------------------------------------------------------------------
 def bench_others(peak_gbs, iters=20, only=None):
-    """only: None (all), or one of 'jagged', 'fp32', 'train', 'nbit'."""
+    """only: None (all), or one of 'jagged', 'fp32', 'train', 'nbit', 'nv12'."""
     res = {}
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device="cuda")
     gen = torch.Generator(device="cuda").manual_seed(99)
@@ -317,6 +317,8 @@ def _others_tbe(res, entry, flush, gen, iters, only):
         _bench_train(entry, flush, gen, iters)
     if only in (None, "nbit"):
         _bench_nbit(entry, flush, gen, iters)
+    if only in (None, "nv12"):
+        _bench_nv12(entry, flush, gen, iters)
     return res
 
 
@@ -365,6 +367,27 @@ def _bench_train(entry, flush, gen, iters):
     ms, _ = time_launches(bwd, iters, flush)
     entry("tbe_fp16_backward_adagrad(config3)", workloads.backward_bytes(inp.num_lookups, U, D * 2, T, B, D, 4),
           ms, inp.num_lookups, {"kernels_per_call": backward_launches(bits)})
+
+
+def _bench_nv12(entry, flush, gen, iters):
+    # the reference plugin's own kernel: one 3840 x 2160 NV12 frame to RGB24, and a batch of 32 such
+    # frames back to back (a decoder's steady state); 1.5 bytes read + 3 written per pixel
+    w, h = 3840, 2160
+    frames = 32
+    y = torch.randint(0, 256, (frames, h, w), dtype=torch.uint8, device="cuda", generator=gen)
+    uv = torch.randint(0, 256, (frames, h // 2, w), dtype=torch.uint8, device="cuda", generator=gen)
+    out = torch.empty((frames, h, w, 3), dtype=torch.uint8, device="cuda")
+    bytes_frame = w * h * 3 // 2 + w * h * 3
+    ms, _ = time_launches(lambda: cabi.nv12_to_rgb(y[0], uv[0], w, h, w, out=out[0]), iters, flush)
+    entry("nv12_to_rgb(4K frame)", bytes_frame, ms, None, {"pixels_per_s": w * h / ms * 1e3})
+
+    def batch():
+        for f in range(frames):
+            cabi.nv12_to_rgb(y[f], uv[f], w, h, w, out=out[f])
+    ms, _ = time_launches(batch, max(3, iters // 4), flush)
+    entry("nv12_to_rgb(32 x 4K frames)", bytes_frame * frames, ms, None,
+          {"pixels_per_s": w * h * frames / ms * 1e3, "launches": frames})
+    del y, uv, out
 
 
 def _bench_nbit(entry, flush, gen, iters):
@@ -420,7 +443,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-others", action="store_true", help="skip the single-kernel configurations")
     ap.add_argument("--small", action="store_true", help="tiny tables, for profiler captures and smoke runs")
-    ap.add_argument("--only", default=None, choices=["jagged", "fp32", "train", "nbit"],
+    ap.add_argument("--only", default=None, choices=["jagged", "fp32", "train", "nbit", "nv12"],
                     help="run one single-GPU configuration alone (few launches; for profiler captures)")
     ap.add_argument("--iters", type=int, default=20, help="timed launches per single-GPU configuration")
     ap.add_argument("--tables", type=int, default=None,

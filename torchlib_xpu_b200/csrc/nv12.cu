@@ -10,7 +10,10 @@
 // pointers / pitch are not 16-byte aligned, take a one-thread-per-pixel path.
 //
 // Arithmetic: every fp32 operation is issued with an explicit round-to-nearest intrinsic in the
-// order the CPU oracle uses, so the two agree bit for bit (no fused multiply-add).
+// order the CPU oracle uses, so the two agree bit for bit (no fused multiply-add). The divisions of
+// the normalisation would make the kernel issue-bound (about 67 instructions per pixel measured),
+// so the block path reads every one-byte term from 256-entry tables built with those same
+// operations (about 28 instructions per pixel).
 #include "common.cuh"
 
 namespace b200tbe {
@@ -76,19 +79,47 @@ __device__ __forceinline__ uint32_t byte_of(uint4 v, int i) {
   return (w >> ((i & 3) * 8)) & 0xffu;
 }
 
+// A byte has 256 values, so every term of the conversion that depends on one byte alone is a table:
+// the normalised luma, and the four non-trivial chroma products (V into R, U and V into G, U into
+// B). The tables are filled per CTA with exactly the operations of pixel_rgb, so a pixel is two
+// shared-memory reads (one for its luma, two 8-byte ones per chroma pair), four adds, and per
+// channel one multiply by 255 and one saturating conversion. The products with the matrix's zeros
+// are +-0 and adding them changes nothing.
+struct Nv12Tables {
+  float luma[256];
+  float2 from_u[256];   // {U into G, U into B}
+  float2 from_v[256];   // {V into R, V into G}
+};
+
+__device__ __forceinline__ void fill_tables(Nv12Tables& t, bool fullrange) {
+  for (int i = threadIdx.x; i < 256; i += blockDim.x) {
+    const float b = static_cast<float>(i);
+    t.luma[i] = __fmul_rn(fullrange ? __fdiv_rn(b, 255.0f) : __fdiv_rn(__fsub_rn(b, 16.0f), 219.0f), 1.0f);
+    const Chroma c = chroma_terms(i, i, fullrange);   // the U and the V term are the same function
+    t.from_u[i] = make_float2(__fmul_rn(c.s1, -0.187324f), __fmul_rn(c.s1, 1.8556f));
+    t.from_v[i] = make_float2(__fmul_rn(c.s2, 1.5748f), __fmul_rn(c.s2, -0.468124f));
+  }
+}
+
+// x * 255 truncated to a byte; the conversion saturates at 0 and 255, which is the clamp.
+__device__ __forceinline__ uint32_t to_byte_sat(float f) {
+  uint32_t r;
+  asm("cvt.rzi.u8.f32 %0, %1;" : "=r"(r) : "f"(__fmul_rn(f, 255.0f)));
+  return r;
+}
+
 // 16 pixels of one row -> 48 bytes, three aligned 16-byte stores.
-__device__ __forceinline__ void convert_row16(uint4 luma, uint4 chroma, bool fullrange, uint8_t* dst) {
+__device__ __forceinline__ void convert_row16(const Nv12Tables& t, uint4 luma, uint4 chroma, uint8_t* dst) {
   uint32_t bytes[48];
 #pragma unroll
   for (int pair = 0; pair < 8; ++pair) {
-    const Chroma c = chroma_terms(byte_of(chroma, 2 * pair), byte_of(chroma, 2 * pair + 1), fullrange);
+    const float2 fu = t.from_u[byte_of(chroma, 2 * pair)], fv = t.from_v[byte_of(chroma, 2 * pair + 1)];
 #pragma unroll
     for (int s = 0; s < 2; ++s) {
-      uint32_t rgb[3];
-      pixel_rgb(byte_of(luma, 2 * pair + s), c, fullrange, rgb);
-      bytes[3 * (2 * pair + s) + 0] = rgb[0];
-      bytes[3 * (2 * pair + s) + 1] = rgb[1];
-      bytes[3 * (2 * pair + s) + 2] = rgb[2];
+      const float s0 = t.luma[byte_of(luma, 2 * pair + s)];
+      bytes[3 * (2 * pair + s) + 0] = to_byte_sat(__fadd_rn(s0, fv.x));
+      bytes[3 * (2 * pair + s) + 1] = to_byte_sat(__fadd_rn(__fadd_rn(s0, fu.x), fv.y));
+      bytes[3 * (2 * pair + s) + 2] = to_byte_sat(__fadd_rn(s0, fu.y));
     }
   }
   uint32_t w[12];
@@ -101,24 +132,33 @@ __device__ __forceinline__ void convert_row16(uint4 luma, uint4 chroma, bool ful
   out[2] = make_uint4(w[8], w[9], w[10], w[11]);
 }
 
+// A plain grid, one block of 16 pixels x 2 rows per thread, 40 registers (measured: a persistent
+// grid striding over one-row blocks with the tables built once per CTA is 17 % slower, forcing 32
+// registers for a single wave on a 4K frame 22 % slower).
 __global__ void __launch_bounds__(kNv12Threads)
     nv12_to_rgb_blocks_kernel(const uint8_t* __restrict__ y_plane, const uint8_t* __restrict__ uv_plane,
                               uint8_t* __restrict__ rgb, int width, int height, int stride,
                               bool fullrange, bool tiled) {
+  __shared__ Nv12Tables tables;
   const int groups = width >> 4;                 // 16-pixel blocks per row
   const int64_t block = static_cast<int64_t>(blockIdx.x) * kNv12Threads + threadIdx.x;
   const int64_t total = static_cast<int64_t>(groups) * ((height + 1) >> 1);
-  if (block >= total) return;
-  const int gy = static_cast<int>(block / groups);
-  const int x = static_cast<int>(block - static_cast<int64_t>(gy) * groups) << 4;
+  const bool mine = block < total;
+  const int gy = mine ? static_cast<int>(block / groups) : 0;
+  const int x = mine ? static_cast<int>(block - static_cast<int64_t>(gy) * groups) << 4 : 0;
   const int y0 = gy * 2;
-  const uint4 chroma = ldg_stream16(uv_plane + surface_offset(x, gy, stride, tiled));
-  const uint4 luma0 = ldg_stream16(y_plane + surface_offset(x, y0, stride, tiled));
-  const bool second = y0 + 1 < height;
-  uint4 luma1 = make_uint4(0u, 0u, 0u, 0u);
+  const bool second = mine && y0 + 1 < height;
+  // the loads are on their way while the tables are filled
+  uint4 chroma = make_uint4(0u, 0u, 0u, 0u), luma0 = chroma, luma1 = chroma;
+  if (mine) {
+    chroma = ldg_stream16(uv_plane + surface_offset(x, gy, stride, tiled));
+    luma0 = ldg_stream16(y_plane + surface_offset(x, y0, stride, tiled));
+  }
   if (second) luma1 = ldg_stream16(y_plane + surface_offset(x, y0 + 1, stride, tiled));
-  convert_row16(luma0, chroma, fullrange, rgb + 3 * (static_cast<size_t>(y0) * width + x));
-  if (second) convert_row16(luma1, chroma, fullrange, rgb + 3 * (static_cast<size_t>(y0 + 1) * width + x));
+  fill_tables(tables, fullrange);
+  __syncthreads();
+  if (mine) convert_row16(tables, luma0, chroma, rgb + 3 * (static_cast<size_t>(y0) * width + x));
+  if (second) convert_row16(tables, luma1, chroma, rgb + 3 * (static_cast<size_t>(y0 + 1) * width + x));
 }
 
 __global__ void __launch_bounds__(kNv12Threads)
