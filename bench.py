@@ -195,11 +195,11 @@ class ShardedTbeStep:
             self.exchange.forward_lookup(self)
 
     def backward(self):
-        grad = self.grad if self.exchange is None else self.exchange.gather_gradients(self)
+        grad, ready = (self.grad, None) if self.exchange is None else self.exchange.gather_gradients_async(self)
         cabi.backward(self.weights, self.weights_offsets, self.D_offsets, self.hash_size_cumsum,
                       self.bits, self.D, self.indices, self.offsets, self.B, grad,
                       cabi.OPT_ROWWISE_ADAGRAD, 0.01, 1e-8, self.momentum, self.momentum_offsets,
-                      scratch=self.scratch)
+                      scratch=self.scratch, grad_ready_event=ready)
 
     def result(self):
         """Pooled rows this rank ends the forward with (its batch slice, all tables, when sharded)."""

@@ -191,6 +191,11 @@ typedef struct {
   void* scratch;                    /* device memory, 256-byte aligned */
   size_t scratch_bytes;
   int32_t* status;
+  void* grad_ready_event;           /* optional cudaEvent_t (NULL: none). The call makes `stream` wait
+                                       for it after linearise, sort and segmentation, just before the
+                                       first kernel that reads grad_output, so a gradient exchange
+                                       running on another stream overlaps the part of the backward
+                                       that needs only the indices. */
 } b200tbe_backward_params;
 
 /* Scratch needed by b200tbe_backward for num_indices lookups with keys of total_hash_size_bits

@@ -104,6 +104,11 @@ def main():
         ref_g = sharded.reference_gradient_exchange(ex.grad_slice)
         torch.cuda.synchronize()
         assert torch.equal(got, ref_g)
+        # the side-stream variant: same rows once its event has fired
+        ex.grad_local.zero_()
+        got2, ready = ex.gather_gradients_async(st)
+        torch.cuda.current_stream().wait_event(ready)
+        assert torch.equal(got2.clone(), ref_g)
     dist.barrier()
     dist.destroy_process_group()
     if rank == 0:

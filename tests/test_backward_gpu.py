@@ -168,3 +168,34 @@ def test_backward_named_training_config_scaled_down():
     mom = np.zeros(T * E, dtype=np.float32)
     _check(T, W, wo, Do, inp.offsets, inp.indices, None, grad, hs, mom, B, np.float16, np.float32,
            oracle.SUM, oracle.ROWWISE_ADAGRAD, lr=0.01)
+
+
+def test_backward_waits_for_the_gradient_event():
+    """grad_ready_event: the gradient matrix is produced on another stream, after a long kernel; the
+    backward started before it is complete still updates with the complete gradients."""
+    rng = workloads.rng_for(470)
+    B = 64
+    case = _backward_case(rng, [300, 200], [64, 128], B, 0, 12, np.float16, np.float32, oracle.SUM,
+                          oracle.ROWWISE_ADAGRAD, False)
+    T, W, wo, Do, offsets, indices, psw, grad, hs, mom = case
+    W_ref, m_ref = W.copy(), mom.copy()
+    oracle.tbe_backward(W_ref, oracle.FP16, wo, Do, hs, B, indices, offsets, grad, m_ref, hs[:-1],
+                        oracle.ROWWISE_ADAGRAD, 0.05, 1e-8, None, oracle.SUM)
+    dW, dm = _dev(W), _dev(mom)
+    src = _dev(grad)
+    dgrad = torch.zeros_like(src)            # wrong until the side stream has written it
+    filler = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    side = torch.cuda.Stream()
+    ready = torch.cuda.Event()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        for _ in range(20):                  # a few milliseconds of work ahead of the gradient copy
+            filler.zero_()
+        dgrad.copy_(src)
+        ready.record(side)
+    bits = max(1, int(hs[-1] - 1).bit_length())
+    cabi.backward(dW, _dev(wo), _dev(Do), _dev(hs), bits, 128, _dev(indices), _dev(offsets), B, dgrad,
+                  oracle.ROWWISE_ADAGRAD, 0.05, 1e-8, dm, _dev(hs[:-1].copy()), grad_ready_event=ready)
+    torch.cuda.synchronize()
+    np.testing.assert_allclose(dW.float().cpu().numpy(), W_ref.astype(np.float32), rtol=RTOL, atol=ATOL)
+    np.testing.assert_allclose(dm.cpu().numpy(), m_ref, rtol=1e-4, atol=1e-6)

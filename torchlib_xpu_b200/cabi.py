@@ -64,6 +64,7 @@ class BackwardParams(ctypes.Structure):
         ("index_bytes", ctypes.c_int32), ("pooling_mode", ctypes.c_int32),
         ("optimizer", ctypes.c_int32), ("learning_rate", ctypes.c_float), ("eps", ctypes.c_float),
         ("scratch", _c_void_p), ("scratch_bytes", ctypes.c_size_t), ("status", _c_void_p),
+        ("grad_ready_event", _c_void_p),
     ]
 
 
@@ -238,7 +239,7 @@ def backward_scratch_bytes(num_indices: int, total_hash_size_bits: int, max_D: i
 def backward(dev_weights, weights_offsets, D_offsets, hash_size_cumsum, total_hash_size_bits, max_D,
              indices, offsets, B, grad_output, optimizer, learning_rate, eps=0.0, momentum1=None,
              momentum1_offsets=None, pooling_mode=POOL_SUM, per_sample_weights=None, scratch=None,
-             status=None, grad_col_offset=0):
+             status=None, grad_col_offset=0, grad_ready_event=None):
     """b200tbe_backward over torch tensors; dev_weights and momentum1 are updated in place."""
     T = weights_offsets.numel()
     n = indices.numel()
@@ -260,6 +261,8 @@ def backward(dev_weights, weights_offsets, D_offsets, hash_size_cumsum, total_ha
     p.learning_rate, p.eps = learning_rate, eps
     p.scratch, p.scratch_bytes = _p(scratch), scratch.numel()
     p.status = _p(status)
+    # a recorded torch.cuda.Event: the gradient matrix is complete once it has fired
+    p.grad_ready_event = grad_ready_event.cuda_event if grad_ready_event is not None else None
     check(lib().b200tbe_backward(ctypes.byref(p), _stream()), "b200tbe_backward")
     return scratch
 

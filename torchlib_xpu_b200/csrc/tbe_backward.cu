@@ -866,6 +866,10 @@ int run_backward(BwdDev d, const b200tbe_backward_params* p, const ScratchLayout
   write_run_starts_kernel<KeyT><<<static_cast<unsigned>(seg_tiles), kSegThreads, 0, stream>>>(
       keys, n, tile_heads, d.counters, d.run_start);
 
+  // everything above needed only the indices; the gradients are read from here on
+  if (p->grad_ready_event != nullptr &&
+      cudaStreamWaitEvent(stream, static_cast<cudaEvent_t>(p->grad_ready_event), 0) != cudaSuccess)
+    return B200TBE_ERR_LAUNCH;
   const int grad_bytes = p->grad_dtype == B200TBE_FP32 ? 4 : 2;
   const int slice_vecs_max = (p->max_D * grad_bytes + 15) / 16;
   const bool w32 = p->weights_dtype == B200TBE_FP32, g32 = p->grad_dtype == B200TBE_FP32;

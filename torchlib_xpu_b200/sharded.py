@@ -116,10 +116,26 @@ class PooledExchange:
         self.barrier()
         return self.grad_local
 
+    def gather_gradients_async(self, step):
+        """The same exchange on a side stream: returns ([B, local_D], event). The event fires when the
+        pull and its barrier are done; pass it to cabi.backward(grad_ready_event=...) and the pull
+        overlaps the linearise + sort part of the backward, which needs only the indices."""
+        main = torch.cuda.current_stream()
+        if getattr(self, "_side", None) is None:
+            self._side = torch.cuda.Stream()
+        start, ready = torch.cuda.Event(), torch.cuda.Event()
+        start.record(main)                     # the peers' gradients are complete in main-stream order
+        self._side.wait_event(start)
+        with torch.cuda.stream(self._side):
+            self.gather_gradients(step)
+            ready.record(self._side)
+        return self.grad_local, ready
+
     def launches_per_step(self) -> int:
         return 1  # the pull kernel (the forward scatter is part of the lookup kernel)
 
     def describe(self) -> str:
         return ("pooled rows stored by the lookup kernel into peer receive buffers (NVLink P2P "
                 "stores); gradients pulled from peers by one copy kernel; NCCL all-reduce of one "
-                "element as the barrier after each")
+                "element as the barrier after each; the pull runs on a side stream under the backward's "
+                "linearise + sort")
