@@ -288,6 +288,27 @@ typedef struct {
 B200TBE_API int b200tbe_exchange_pull(const b200tbe_exchange_pull_params* p,
                                       b200tbe_stream_t stream);
 
+/* The same exchange as a push, which is what NVLink prefers (stores stream, loads wait): src is this
+ * rank's gradient matrix, rows x (num_dsts * block_bytes) with rows src_stride_bytes apart; column
+ * block d of row r is stored at row dst_row_offset + r of destination d's matrix (rows
+ * dst_stride_bytes apart, block_bytes wide; peer-mapped or local). Byte counts and pointers are
+ * multiples of 16. The caller orders the call after the destinations' previous readers and orders
+ * the destinations' next readers after it (stream-ordered barriers). No counterpart in the
+ * reference, like the pull. */
+typedef struct {
+  const void* src;
+  void* dsts[B200TBE_MAX_DESTS];
+  int64_t src_stride_bytes;
+  int64_t dst_stride_bytes;
+  int64_t dst_row_offset;
+  int64_t rows;
+  int64_t block_bytes;
+  int32_t num_dsts;
+} b200tbe_exchange_push_params;
+
+B200TBE_API int b200tbe_exchange_push(const b200tbe_exchange_push_params* p,
+                                      b200tbe_stream_t stream);
+
 /* ------------------------------------------------------------------------------------------------
  * Jagged tensors. values is [total_rows, inner_size]; dense is [outer_size, max_lengths[0], ...,
  * max_lengths[n-1], inner_size]; offsets[d] is the d-th level's offsets array (offsets[0] has

@@ -104,8 +104,13 @@ def main():
         ref_g = sharded.reference_gradient_exchange(ex.grad_slice)
         torch.cuda.synchronize()
         assert torch.equal(got, ref_g)
+        # the pull moves the same rows
+        ex.grad_local.zero_()
+        ex.barrier()
+        assert torch.equal(ex.gather_gradients(st, push=False).clone(), ref_g)
         # the side-stream variant: same rows once its event has fired
         ex.grad_local.zero_()
+        ex.barrier()                     # no peer stores into a matrix that is still being cleared
         got2, ready = ex.gather_gradients_async(st)
         torch.cuda.current_stream().wait_event(ready)
         assert torch.equal(got2.clone(), ref_g)

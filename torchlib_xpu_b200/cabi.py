@@ -76,6 +76,14 @@ class ExchangePullParams(ctypes.Structure):
     ]
 
 
+class ExchangePushParams(ctypes.Structure):
+    _fields_ = [
+        ("src", _c_void_p), ("dsts", _c_void_p * MAX_DESTS), ("src_stride_bytes", ctypes.c_int64),
+        ("dst_stride_bytes", ctypes.c_int64), ("dst_row_offset", ctypes.c_int64), ("rows", ctypes.c_int64),
+        ("block_bytes", ctypes.c_int64), ("num_dsts", ctypes.c_int32),
+    ]
+
+
 class JaggedShape(ctypes.Structure):
     _fields_ = [
         ("offsets", _c_void_p * MAX_JAGGED_DIMS), ("max_lengths", ctypes.c_int64 * MAX_JAGGED_DIMS),
@@ -90,7 +98,7 @@ EXPORTS = (
     "b200tbe_status_string", "b200tbe_abi_version", "b200tbe_forward", "b200tbe_nbit_forward",
     "b200tbe_backward_scratch_bytes", "b200tbe_backward", "b200tbe_radix_sort_scratch_bytes",
     "b200tbe_radix_sort_pairs", "b200tbe_radix_sort_pairs_static_max",
-    "b200tbe_radix_sort_pairs_static", "b200tbe_exchange_pull", "b200tbe_quantized_row_bytes",
+    "b200tbe_radix_sort_pairs_static", "b200tbe_exchange_pull", "b200tbe_exchange_push", "b200tbe_quantized_row_bytes",
     "b200tbe_quantize_rows", "b200tbe_dequantize_rows", "b200tbe_nv12_to_rgb", "b200tbe_jagged_to_padded_dense", "b200tbe_dense_to_jagged",
     "b200tbe_jagged_dense_elementwise_add",
 )
@@ -128,6 +136,7 @@ def lib() -> ctypes.CDLL:
             _c_void_p, _c_void_p, _c_void_p, _c_void_p, ctypes.c_int64, ctypes.c_int32,
             ctypes.c_int32, _c_void_p]
         _lib.b200tbe_exchange_pull.argtypes = [ctypes.POINTER(ExchangePullParams), _c_void_p]
+        _lib.b200tbe_exchange_push.argtypes = [ctypes.POINTER(ExchangePushParams), _c_void_p]
         _lib.b200tbe_quantized_row_bytes.restype = ctypes.c_int64
         _lib.b200tbe_quantized_row_bytes.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
         _lib.b200tbe_quantize_rows.argtypes = [
@@ -291,6 +300,19 @@ def exchange_pull(src_ptrs, dst, src_stride_bytes, src_col_offset_bytes, rows_pe
     p.dst_stride_bytes = dst.stride(0) * dst.element_size()
     p.rows_per_src, p.row_bytes, p.num_srcs = rows_per_src, row_bytes, len(src_ptrs)
     check(lib().b200tbe_exchange_pull(ctypes.byref(p), _stream()), "b200tbe_exchange_pull")
+
+
+def exchange_push(src, dst_ptrs, dst_stride_bytes, dst_row_offset, block_bytes):
+    """b200tbe_exchange_push: src is a [rows, len(dst_ptrs) * block] tensor, dst_ptrs raw device
+    addresses of the destinations' matrices (peer-mapped buffers)."""
+    p = ExchangePushParams()
+    p.src = _p(src)
+    for i, ptr in enumerate(dst_ptrs):
+        p.dsts[i] = int(ptr)
+    p.src_stride_bytes = src.stride(0) * src.element_size()
+    p.dst_stride_bytes, p.dst_row_offset = dst_stride_bytes, dst_row_offset
+    p.rows, p.block_bytes, p.num_dsts = src.shape[0], block_bytes, len(dst_ptrs)
+    check(lib().b200tbe_exchange_push(ctypes.byref(p), _stream()), "b200tbe_exchange_push")
 
 
 def quantize_rows(src, ty, row_alignment=16, header_first=True):

@@ -8,8 +8,9 @@ up with the pooled rows of its own slice of the batch (B / G bags) for ALL table
 (with tables dealt round-robin, global table id = local_table * G + rank). The exchange is not a
 separate collective on the forward path: b200tbe_forward writes each pooled vector straight into the
 destination rank's receive buffer through its peer mapping (plain 16-byte stores over NVLink), and a
-stream-ordered barrier closes the step. On the way back each rank pulls its tables' column block of
-every peer's gradient matrix with b200tbe_exchange_pull, then runs the local fused backward.
+stream-ordered barrier closes the step. On the way back each rank stores the column blocks of its
+gradient rows into the owning ranks' matrices with b200tbe_exchange_push (b200tbe_exchange_pull
+moves the same bytes the other way round, slower), then runs the local fused backward.
 
 `layout_*` below are pure index arithmetic and are what the CPU (gloo) tests exercise;
 `reference_exchange` is the same data movement as an all_to_all_single, used as the baseline on
@@ -83,7 +84,10 @@ class PooledExchange:
         self._grad_hdl = symm_mem.rendezvous(self.grad_slice, dist.group.WORLD)
         self.recv_ptrs = [int(p) for p in self._recv_hdl.buffer_ptrs]
         self.grad_ptrs = [int(p) for p in self._grad_hdl.buffer_ptrs]
-        self.grad_local = torch.empty((B, local_D), dtype=dtype, device=dev)
+        # this rank's column block of every rank's gradients; the peers store into it
+        self.grad_local = symm_mem.empty((B, local_D), dtype=dtype, device=dev)
+        self._gradl_hdl = symm_mem.rendezvous(self.grad_local, dist.group.WORLD)
+        self.gradl_ptrs = [int(p) for p in self._gradl_hdl.buffer_ptrs]
         self._token = torch.zeros(1, device=dev)
         gen = torch.Generator(device=dev).manual_seed(4242 + rank)
         self.grad_slice.copy_(torch.randn((self.per, world * local_D), device=dev, generator=gen).to(dtype))
@@ -106,19 +110,27 @@ class PooledExchange:
                      output_dtype=self.dtype)
         self.barrier()
 
-    def gather_gradients(self, step):
-        """Pulls this rank's column block of every peer's gradient matrix; returns [B, local_D]."""
+    def gather_gradients(self, step, push: bool = True):
+        """Brings this rank's column block of every rank's gradient matrix into [B, local_D]. Every
+        rank stores the blocks of its own gradient rows into the owners' matrices (push: NVLink
+        stores stream, measured twice as fast as pulling the same bytes); push=False pulls instead.
+        The call must follow a barrier that follows the previous reader of grad_local on every rank
+        (the forward's barrier does), and ends with one."""
         from . import cabi
 
         esz = self.grad_slice.element_size()
-        cabi.exchange_pull(self.grad_ptrs, self.grad_local, self.world * self.local_D * esz,
-                           self.rank * self.local_D * esz, self.per, self.local_D * esz)
+        if push:
+            cabi.exchange_push(self.grad_slice, self.gradl_ptrs, self.local_D * esz, self.rank * self.per,
+                               self.local_D * esz)
+        else:
+            cabi.exchange_pull(self.grad_ptrs, self.grad_local, self.world * self.local_D * esz,
+                               self.rank * self.local_D * esz, self.per, self.local_D * esz)
         self.barrier()
         return self.grad_local
 
     def gather_gradients_async(self, step):
         """The same exchange on a side stream: returns ([B, local_D], event). The event fires when the
-        pull and its barrier are done; pass it to cabi.backward(grad_ready_event=...) and the pull
+        exchange and its barrier are done; pass it to cabi.backward(grad_ready_event=...) and it
         overlaps the linearise + sort part of the backward, which needs only the indices."""
         main = torch.cuda.current_stream()
         if getattr(self, "_side", None) is None:
@@ -132,10 +144,10 @@ class PooledExchange:
         return self.grad_local, ready
 
     def launches_per_step(self) -> int:
-        return 1  # the pull kernel (the forward scatter is part of the lookup kernel)
+        return 1  # the gradient push kernel (the forward scatter is part of the lookup kernel)
 
     def describe(self) -> str:
         return ("pooled rows stored by the lookup kernel into peer receive buffers (NVLink P2P "
-                "stores); gradients pulled from peers by one copy kernel; NCCL all-reduce of one "
-                "element as the barrier after each; the pull runs on a side stream under the backward's "
-                "linearise + sort")
+                "stores); gradient blocks pushed to their owners by one copy kernel; NCCL all-reduce of "
+                "one element as the barrier after each; the push runs on a side stream under the "
+                "backward's linearise + sort")
