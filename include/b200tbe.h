@@ -310,6 +310,22 @@ B200TBE_API int b200tbe_exchange_push(const b200tbe_exchange_push_params* p,
                                       b200tbe_stream_t stream);
 
 /* ------------------------------------------------------------------------------------------------
+ * Segment permutation of jagged data (the data movement of torch.ops.fbgemm.permute_2D_sparse_data
+ * and of the input distribution of a table-wise sharded lookup, where ids arrive grouped by source
+ * rank and are regrouped by table): out segment j = in segment perm[j].
+ * in_offsets[num_segments + 1] are the starts of the input segments, out_offsets[num_segments + 1]
+ * the starts of the output segments (the caller computes them as the exclusive sum of the permuted
+ * lengths; out_offsets[num_segments] = total_elems). Elements are moved as raw bytes: elem_bytes 2,
+ * 4 or 8 (ids, per-sample weights). offset_bytes and perm_bytes are 4 or 8. No counterpart in the
+ * reference.
+ * ---------------------------------------------------------------------------------------------- */
+B200TBE_API int b200tbe_permute_segments(const void* in, void* out, const void* in_offsets,
+                                         const void* out_offsets, const void* perm,
+                                         int64_t num_segments, int64_t total_elems, int32_t elem_bytes,
+                                         int32_t offset_bytes, int32_t perm_bytes,
+                                         b200tbe_stream_t stream);
+
+/* ------------------------------------------------------------------------------------------------
  * Jagged tensors. values is [total_rows, inner_size]; dense is [outer_size, max_lengths[0], ...,
  * max_lengths[n-1], inner_size]; offsets[d] is the d-th level's offsets array (offsets[0] has
  * outer_size + 1 entries). Elements are moved as raw bytes, so any dtype of elem_bytes 1, 2, 4 or 8

@@ -54,6 +54,35 @@ def expected_slice(rank, world, T, D, B, full):
     return np.concatenate(cols, axis=1)
 
 
+def check_input_distribution(rank, world, T, B, offsets, indices, offl, idxl, device, fns):
+    """Every rank starts with its slice of the batch for ALL tables (the data-parallel layout) and
+    must end with ALL samples for its own tables, in the bag order the lookup reads."""
+    r0, r1 = sharded.layout_batch_rows(rank, world, B)
+    per = r1 - r0
+    lengths_dp = np.zeros((T, per), dtype=np.int64)
+    parts = []
+    for t in range(T):
+        for bl in range(per):
+            a, b = int(offsets[t * B + r0 + bl]), int(offsets[t * B + r0 + bl + 1])
+            lengths_dp[t, bl] = b - a
+            parts.append(indices[a:b])
+    ids_dp = np.concatenate(parts).astype(np.int64) if parts else np.zeros(0, dtype=np.int64)
+    w_dp = (ids_dp % 7).astype(np.float32) * 0.25
+    to = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device)
+    T_local = T // world
+    for fn in fns:
+        lengths_tw, offsets_tw, ids_tw, w_tw = fn(to(lengths_dp), to(ids_dp), to(w_dp))
+        assert lengths_tw.shape == (T_local, B)
+        np.testing.assert_array_equal(offsets_tw.cpu().numpy(), offl)
+        np.testing.assert_array_equal(ids_tw.cpu().numpy(), idxl)
+        np.testing.assert_array_equal(w_tw.cpu().numpy(), (idxl % 7).astype(np.float32) * 0.25)
+        # without weights, and with 32-bit ids
+        _, off2, ids2, none = fn(to(lengths_dp), to(ids_dp.astype(np.int32)))
+        assert none is None and ids2.dtype == torch.int32
+        np.testing.assert_array_equal(ids2.cpu().numpy(), idxl)
+        np.testing.assert_array_equal(off2.cpu().numpy(), offl)
+
+
 def main():
     backend = sys.argv[1]
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -68,6 +97,8 @@ def main():
     local_D = len(mine) * D
 
     if backend == "gloo":
+        check_input_distribution(rank, world, T, B, offsets, indices, offl, idxl, "cpu",
+                                 [sharded.reference_distribute_inputs])
         pooled_local = torch.from_numpy(oracle.tbe_forward(Wl, oracle.FP16, wol, Dol, B, idxl, offl))
         got = sharded.reference_exchange(pooled_local)
         assert got.shape == (B // world, world * local_D)
@@ -81,6 +112,9 @@ def main():
             np.testing.assert_array_equal(back[s * per:(s + 1) * per].numpy(), exp[s * per:(s + 1) * per] * (s + 1))
     else:
         from torchlib_xpu_b200 import cabi
+
+        check_input_distribution(rank, world, T, B, offsets, indices, offl, idxl, "cuda",
+                                 [sharded.reference_distribute_inputs, sharded.distribute_inputs])
 
         class Step:
             pass

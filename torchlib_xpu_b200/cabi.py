@@ -98,7 +98,7 @@ EXPORTS = (
     "b200tbe_status_string", "b200tbe_abi_version", "b200tbe_forward", "b200tbe_nbit_forward",
     "b200tbe_backward_scratch_bytes", "b200tbe_backward", "b200tbe_radix_sort_scratch_bytes",
     "b200tbe_radix_sort_pairs", "b200tbe_radix_sort_pairs_static_max",
-    "b200tbe_radix_sort_pairs_static", "b200tbe_exchange_pull", "b200tbe_exchange_push", "b200tbe_quantized_row_bytes",
+    "b200tbe_radix_sort_pairs_static", "b200tbe_exchange_pull", "b200tbe_exchange_push", "b200tbe_permute_segments", "b200tbe_quantized_row_bytes",
     "b200tbe_quantize_rows", "b200tbe_dequantize_rows", "b200tbe_nv12_to_rgb", "b200tbe_jagged_to_padded_dense", "b200tbe_dense_to_jagged",
     "b200tbe_jagged_dense_elementwise_add",
 )
@@ -137,6 +137,8 @@ def lib() -> ctypes.CDLL:
             ctypes.c_int32, _c_void_p]
         _lib.b200tbe_exchange_pull.argtypes = [ctypes.POINTER(ExchangePullParams), _c_void_p]
         _lib.b200tbe_exchange_push.argtypes = [ctypes.POINTER(ExchangePushParams), _c_void_p]
+        _lib.b200tbe_permute_segments.argtypes = [_c_void_p] * 5 + [ctypes.c_int64, ctypes.c_int64] + \
+            [ctypes.c_int32] * 3 + [_c_void_p]
         _lib.b200tbe_quantized_row_bytes.restype = ctypes.c_int64
         _lib.b200tbe_quantized_row_bytes.argtypes = [ctypes.c_int32, ctypes.c_int32, ctypes.c_int32]
         _lib.b200tbe_quantize_rows.argtypes = [
@@ -313,6 +315,18 @@ def exchange_push(src, dst_ptrs, dst_stride_bytes, dst_row_offset, block_bytes):
     p.dst_stride_bytes, p.dst_row_offset = dst_stride_bytes, dst_row_offset
     p.rows, p.block_bytes, p.num_dsts = src.shape[0], block_bytes, len(dst_ptrs)
     check(lib().b200tbe_exchange_push(ctypes.byref(p), _stream()), "b200tbe_exchange_push")
+
+
+def permute_segments(values, in_offsets, out_offsets, perm):
+    """b200tbe_permute_segments: out segment j = in segment perm[j]; values is a flat tensor of 2-,
+    4- or 8-byte elements, the offsets int32/int64 tensors of num_segments + 1 entries."""
+    out = torch.empty_like(values)
+    n = perm.numel()
+    check(lib().b200tbe_permute_segments(_p(values), _p(out), _p(in_offsets), _p(out_offsets), _p(perm), n,
+                                         values.numel(), values.element_size(), in_offsets.element_size(),
+                                         perm.element_size(), _stream()),
+          "b200tbe_permute_segments")
+    return out
 
 
 def quantize_rows(src, ty, row_alignment=16, header_first=True):

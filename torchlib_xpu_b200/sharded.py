@@ -151,3 +151,93 @@ class PooledExchange:
                 "stores); gradient blocks pushed to their owners by one copy kernel; NCCL all-reduce of "
                 "one element as the barrier after each; the push runs on a side stream under the "
                 "backward's linearise + sort")
+
+
+# ---- input distribution: data-parallel batches -> table-wise layout ------------------------------
+def destination_major_tables(world: int, total_tables: int) -> list[int]:
+    """Global table ids ordered by owning rank, each rank's tables in its local order."""
+    return [t for d in range(world) for t in local_tables(d, world, total_tables)]
+
+
+def _exclusive_offsets(lengths_flat: torch.Tensor) -> torch.Tensor:
+    off = torch.zeros(lengths_flat.numel() + 1, dtype=torch.int64, device=lengths_flat.device)
+    torch.cumsum(lengths_flat, 0, out=off[1:])
+    return off
+
+
+def reference_permute_segments(values, lengths_flat, perm):
+    """out segment j = in segment perm[j], in plain torch (any device): the checker of
+    b200tbe_permute_segments and the data movement of the CPU (gloo) tests."""
+    in_off = _exclusive_offsets(lengths_flat)
+    out_len = lengths_flat[perm]
+    out_off = _exclusive_offsets(out_len)
+    shift = in_off[:-1][perm] - out_off[:-1]
+    src = torch.arange(values.numel(), device=values.device) + torch.repeat_interleave(shift, out_len)
+    return values[src]
+
+
+def kernel_permute_segments(values, lengths_flat, perm):
+    """The same through b200tbe_permute_segments (CUDA tensors only)."""
+    from . import cabi
+
+    if not values.is_cuda:
+        raise RuntimeError("kernel_permute_segments needs CUDA tensors; there is no CPU path")
+    lengths_flat = lengths_flat.to(torch.int64)
+    perm = perm.to(torch.int64)
+    in_off = _exclusive_offsets(lengths_flat)
+    out_off = _exclusive_offsets(lengths_flat[perm])
+    return cabi.permute_segments(values.contiguous(), in_off, out_off, perm)
+
+
+def _distribute(lengths_dp, indices_dp, weights_dp, group, permute):
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    T_global, per = lengths_dp.shape
+    if T_global % world != 0:
+        raise ValueError("%d tables cannot be dealt to %d ranks evenly" % (T_global, world))
+    T_local = T_global // world
+    dev = lengths_dp.device
+    lengths_dp = lengths_dp.to(torch.int64)
+    order = torch.tensor(destination_major_tables(world, T_global), dtype=torch.int64, device=dev)
+    # 1. this rank's ids regrouped by destination rank (whole tables move as segments)
+    table_len = lengths_dp.sum(1)
+    send_lengths = lengths_dp[order].contiguous()
+    send = [permute(indices_dp, table_len, order)]
+    if weights_dp is not None:
+        send.append(permute(weights_dp, table_len, order))
+    # 2. bag lengths first: they say how many ids each peer will send
+    recv_lengths = torch.empty_like(send_lengths)
+    dist.all_to_all_single(recv_lengths, send_lengths, group=group)
+    send_splits = table_len[order].view(world, T_local).sum(1).tolist()
+    recv_splits = recv_lengths.view(world, T_local * per).sum(1).tolist()
+    recv = []
+    for buf in send:
+        got = torch.empty(int(sum(recv_splits)), dtype=buf.dtype, device=dev)
+        dist.all_to_all_single(got, buf, recv_splits, send_splits, group=group)
+        recv.append(got)
+    # 3. received as (source rank, local table, sample); the lookup wants (local table, global sample)
+    seg = torch.arange(world * T_local * per, device=dev).view(world, T_local, per)
+    perm = seg.permute(1, 0, 2).reshape(-1)
+    lengths_tw = recv_lengths.view(world, T_local, per).permute(1, 0, 2).reshape(T_local, world * per)
+    flat = recv_lengths.view(-1)
+    indices_tw = permute(recv[0], flat, perm)
+    weights_tw = permute(recv[1], flat, perm) if weights_dp is not None else None
+    offsets_tw = _exclusive_offsets(lengths_tw.reshape(-1))
+    return lengths_tw, offsets_tw, indices_tw, weights_tw
+
+
+def distribute_inputs(lengths_dp, indices_dp, weights_dp=None, group=None):
+    """From the data-parallel layout to the table-wise one (CUDA tensors, NCCL).
+
+    lengths_dp [T_global, B / G]: bag lengths of this rank's slice of the global batch for every
+    table; indices_dp (and optional per-sample weights_dp): the ids in table-major, sample-minor
+    order. Returns, for the tables this rank owns and ALL B samples: lengths [T_local, B], offsets
+    [T_local * B + 1], ids and weights in bag order: the arguments of b200tbe_forward /
+    b200tbe_backward. Two all_to_all_single calls (lengths, then ids with the sizes the lengths
+    announce; one host read of the split sizes in between) and two segment permutations by
+    b200tbe_permute_segments."""
+    return _distribute(lengths_dp, indices_dp, weights_dp, group, kernel_permute_segments)
+
+
+def reference_distribute_inputs(lengths_dp, indices_dp, weights_dp=None, group=None):
+    """The same in plain torch on any backend (gloo on CPU): the checker."""
+    return _distribute(lengths_dp, indices_dp, weights_dp, group, reference_permute_segments)
