@@ -121,3 +121,26 @@ def test_nbit_lookup_op():
     assert out.dtype == torch.float16
     want = oracle.nbit_forward(W, wo, tys_a, Do, 16, B, indices, offsets)
     np.testing.assert_allclose(out.float().cpu().numpy(), want, rtol=1e-3, atol=1e-3)
+
+
+def test_permute_2d_sparse_data_rows_may_repeat_or_drop():
+    """torch.ops.fbgemm.permute_2D_sparse_data: row j of the result is row permute[j] of the input."""
+    rng = workloads.rng_for(1400)
+    T, B = 6, 37
+    lengths = rng.integers(0, 9, size=(T, B)).astype(np.int64)
+    total = int(lengths.sum())
+    indices = rng.integers(0, 1 << 40, size=total, dtype=np.int64)
+    weights = rng.standard_normal(total).astype(np.float32)
+    permute = np.array([4, 0, 0, 5, 2], dtype=np.int32)      # row 0 twice, rows 1 and 3 dropped
+    row_start = np.concatenate([[0], np.cumsum(lengths.sum(1))])
+    want_idx = np.concatenate([indices[row_start[t]:row_start[t + 1]] for t in permute])
+    want_w = np.concatenate([weights[row_start[t]:row_start[t + 1]] for t in permute])
+    dev = lambda a: torch.from_numpy(a).cuda()
+    pl, pi, pw = torch.ops.fbgemm.permute_2D_sparse_data(dev(permute), dev(lengths), dev(indices), dev(weights), None)
+    assert np.array_equal(pl.cpu().numpy(), lengths[permute])
+    assert np.array_equal(pi.cpu().numpy(), want_idx)
+    assert np.array_equal(pw.cpu().numpy(), want_w)
+    pl2, pi2, none = torch.ops.fbgemm.permute_2D_sparse_data(dev(permute.astype(np.int64)), dev(lengths.astype(np.int32)),
+                                                             dev(indices.astype(np.int32)), None, int(want_idx.size))
+    assert none is None and np.array_equal(pi2.cpu().numpy(), want_idx.astype(np.int32))
+    assert np.array_equal(pl2.cpu().numpy(), lengths[permute].astype(np.int32))

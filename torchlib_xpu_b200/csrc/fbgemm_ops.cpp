@@ -173,6 +173,55 @@ Tensor jagged_2d_to_dense(const Tensor& values, const Tensor& offsets, int64_t m
   return jagged_to_padded_dense(values, {offsets}, {max_sequence_length}, 0.0);
 }
 
+// ---- permute_2D_sparse_data -----------------------------------------------------------------------
+// lengths is [T, B], indices (and weights) hold the T rows' ids one row after the other; row j of
+// the result is row permute[j] of the input (rows may repeat or be left out, so the result can be
+// longer or shorter than the input). Whole rows move as segments of b200tbe_permute_segments.
+std::tuple<Tensor, Tensor, c10::optional<Tensor>> permute_2d_sparse_data(
+    const Tensor& permute, const Tensor& lengths, const Tensor& indices,
+    const c10::optional<Tensor>& weights, c10::optional<int64_t> permuted_lengths_sum) {
+  check_cuda_contig(permute, "permute");
+  check_cuda_contig(lengths, "lengths");
+  check_cuda_contig(indices, "indices");
+  TORCH_CHECK(lengths.dim() == 2, "lengths must be [T, B]");
+  TORCH_CHECK(permute.scalar_type() == at::kInt || permute.scalar_type() == at::kLong,
+              "permute must be int32 or int64");
+  c10::cuda::CUDAGuard guard(indices.device());
+  const Tensor permuted_lengths = lengths.index_select(0, permute);
+  const Tensor row_len = lengths.to(at::kLong).sum(1);
+  Tensor in_off = at::zeros({row_len.numel() + 1}, row_len.options());
+  in_off.slice(0, 1).copy_(row_len.cumsum(0));
+  const Tensor out_len = row_len.index_select(0, permute);
+  Tensor out_off = at::zeros({out_len.numel() + 1}, out_len.options());
+  out_off.slice(0, 1).copy_(out_len.cumsum(0));
+  int64_t total = 0;
+  if (permuted_lengths_sum.has_value()) {
+    total = *permuted_lengths_sum;
+  } else {
+    total = out_off[-1].item<int64_t>();  // one synchronising read, as in fbgemm_gpu
+  }
+  TORCH_CHECK(total >= 0, "permuted_lengths_sum must be non-negative");
+  auto move = [&](const Tensor& src, const char* what) {
+    Tensor dst = at::empty({total}, src.options());
+    const int64_t eb = static_cast<int64_t>(src.element_size());
+    TORCH_CHECK(eb == 2 || eb == 4 || eb == 8, what, ": elements of 2, 4 or 8 bytes");
+    check_status(b200tbe_permute_segments(src.data_ptr(), dst.data_ptr(), in_off.data_ptr(),
+                                          out_off.data_ptr(), permute.data_ptr(), permute.numel(),
+                                          total, static_cast<int32_t>(eb), 8,
+                                          static_cast<int32_t>(permute.element_size()), current_stream()),
+                 "permute_2D_sparse_data");
+    return dst;
+  };
+  Tensor permuted_indices = move(indices, "indices");
+  c10::optional<Tensor> permuted_weights;
+  if (weights.has_value() && weights->defined()) {
+    check_cuda_contig(*weights, "weights");
+    TORCH_CHECK(weights->numel() == indices.numel(), "weights and indices differ in length");
+    permuted_weights = move(*weights, "weights");
+  }
+  return {permuted_lengths, permuted_indices, permuted_weights};
+}
+
 // ---- TBE forward / backward -----------------------------------------------------------------
 
 struct TbeCommon {
@@ -527,6 +576,9 @@ TORCH_LIBRARY_FRAGMENT(fbgemm, m) {
   m.def("dense_to_jagged(Tensor dense, Tensor[] x_offsets, int? total_L=None) -> (Tensor, Tensor[])");
   m.def("jagged_dense_elementwise_add(Tensor x_values, Tensor[] x_offsets, Tensor y) -> Tensor");
   m.def("jagged_2d_to_dense(Tensor values, Tensor offsets, int max_sequence_length) -> Tensor");
+  m.def(
+      "permute_2D_sparse_data(Tensor permute, Tensor lengths, Tensor indices, Tensor? weights=None, "
+      "int? permuted_lengths_sum=None) -> (Tensor, Tensor, Tensor?)");
   m.def("FloatToFusedNBitRowwiseQuantizedSBHalf(Tensor input, int bit_rate) -> Tensor");
   m.def("HalfToFusedNBitRowwiseQuantizedSBHalf(Tensor input, int bit_rate) -> Tensor");
   m.def("FloatOrHalfToFusedNBitRowwiseQuantizedSBHalf(Tensor input, int bit_rate) -> Tensor");
@@ -568,6 +620,7 @@ TORCH_LIBRARY_IMPL(fbgemm, CUDA, m) {
   m.impl("dense_to_jagged", TORCH_FN(dense_to_jagged));
   m.impl("jagged_dense_elementwise_add", TORCH_FN(jagged_dense_elementwise_add));
   m.impl("jagged_2d_to_dense", TORCH_FN(jagged_2d_to_dense));
+  m.impl("permute_2D_sparse_data", TORCH_FN(permute_2d_sparse_data));
   m.impl("FloatToFusedNBitRowwiseQuantizedSBHalf", TORCH_FN(float_or_half_to_fused_nbit));
   m.impl("HalfToFusedNBitRowwiseQuantizedSBHalf", TORCH_FN(float_or_half_to_fused_nbit));
   m.impl("FloatOrHalfToFusedNBitRowwiseQuantizedSBHalf", TORCH_FN(float_or_half_to_fused_nbit));
