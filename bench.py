@@ -274,7 +274,7 @@ def reference_arm(args, cfg, rank, json_out):
 # The other named configurations, single GPU, one kernel (or kernel group) each
 # --------------------------------------------------------------------------------------------
 def bench_others(peak_gbs, iters=20, only=None):
-    """only: None (all), or one of 'jagged', 'fp32', 'train', 'nbit', 'nv12'."""
+    """only: None (all), or one of 'jagged', 'fp32', 'train', 'nbit', 'nv12', 'permute'."""
     res = {}
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device="cuda")
     gen = torch.Generator(device="cuda").manual_seed(99)
@@ -319,6 +319,8 @@ def _others_tbe(res, entry, flush, gen, iters, only):
         _bench_nbit(entry, flush, gen, iters)
     if only in (None, "nv12"):
         _bench_nv12(entry, flush, gen, iters)
+    if only in (None, "permute"):
+        _bench_permute(entry, flush, gen, iters)
     return res
 
 
@@ -367,6 +369,27 @@ def _bench_train(entry, flush, gen, iters):
     ms, _ = time_launches(bwd, iters, flush)
     entry("tbe_fp16_backward_adagrad(config3)", workloads.backward_bytes(inp.num_lookups, U, D * 2, T, B, D, 4),
           ms, inp.num_lookups, {"kernels_per_call": backward_launches(bits)})
+
+
+def _bench_permute(entry, flush, gen, iters):
+    # the regrouping step of the input distribution at the bench step's shape: what one rank of 8
+    # receives, (source rank, local table, sample) -> (local table, global sample): 4.2 M bags,
+    # about 107 M int64 ids; every id is read once and written once
+    from torchlib_xpu_b200 import sharded
+    world, T_local, B = 8, 64, 65536
+    per = B // world
+    lengths = torch.randint(1, 51, (world * T_local * per,), device="cuda", generator=gen)
+    n = int(lengths.sum().item())
+    ids = torch.randint(0, 4_000_000, (n,), device="cuda", generator=gen)
+    perm = torch.arange(world * T_local * per, device="cuda").view(world, T_local, per).permute(1, 0, 2).reshape(-1)
+    in_off = torch.zeros(lengths.numel() + 1, dtype=torch.int64, device="cuda")
+    torch.cumsum(lengths, 0, out=in_off[1:])
+    out_off = torch.zeros_like(in_off)
+    torch.cumsum(lengths[perm], 0, out=out_off[1:])
+    ms, _ = time_launches(lambda: cabi.permute_segments(ids, in_off, out_off, perm), max(3, iters // 2), flush)
+    entry("permute_segments(config5 ids, 8 ranks)", 2 * n * 8 + 3 * lengths.numel() * 8, ms, n,
+          {"segments": int(lengths.numel())})
+    del ids, lengths, perm, in_off, out_off
 
 
 def _bench_nv12(entry, flush, gen, iters):
@@ -443,7 +466,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-others", action="store_true", help="skip the single-kernel configurations")
     ap.add_argument("--small", action="store_true", help="tiny tables, for profiler captures and smoke runs")
-    ap.add_argument("--only", default=None, choices=["jagged", "fp32", "train", "nbit", "nv12"],
+    ap.add_argument("--only", default=None, choices=["jagged", "fp32", "train", "nbit", "nv12", "permute"],
                     help="run one single-GPU configuration alone (few launches; for profiler captures)")
     ap.add_argument("--iters", type=int, default=20, help="timed launches per single-GPU configuration")
     ap.add_argument("--tables", type=int, default=None,

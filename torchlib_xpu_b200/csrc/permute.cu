@@ -4,7 +4,7 @@
 //
 // Segments range from empty bags to whole tables, so the work is split by output ELEMENT, not by
 // segment: a CTA owns a tile of consecutive output elements, finds the segment of its first element
-// by binary search over the output offsets, walks the segment boundaries of the tile into shared
+// by a CTA-wide 256-ary search over the output offsets, walks the segment boundaries of the tile into shared
 // memory once, and then every thread copies elements whose source position is the input start of
 // their segment plus their distance from its output start. Reads and writes are coalesced inside
 // a segment; per element the traffic is its bytes in and out plus one shared-memory lookup.
@@ -49,7 +49,20 @@ __global__ void __launch_bounds__(kPermThreads)
   __shared__ int64_t first_seg;
   const int64_t tile0 = static_cast<int64_t>(blockIdx.x) * kPermTile;
   const int64_t tile1 = tile0 + kPermTile < total ? tile0 + kPermTile : total;
-  if (threadIdx.x == 0) first_seg = segment_of<OffT>(out_offsets, num_segments, tile0);
+  {
+    // the segment of the tile's first element, searched by the whole CTA: 256 probes per round
+    // narrow the range 256-fold, so 22 bits of segments take 3 dependent loads instead of 22
+    int64_t lo = 0, n = num_segments;
+    while (n > 1) {
+      const int64_t step = (n + kPermThreads - 1) / kPermThreads;
+      const int64_t probe = (static_cast<int64_t>(threadIdx.x) + 1) * step;
+      const bool le = probe < n && load_off<OffT>(out_offsets, lo + probe) <= tile0;
+      const int64_t c = __syncthreads_count(le);   // the offsets are sorted: the true probes are the first c
+      lo += c * step;
+      n = n - c * step < step ? n - c * step : step;
+    }
+    if (threadIdx.x == 0) first_seg = lo;
+  }
   __syncthreads();
   // the non-empty segments that intersect the tile, in order; threads take candidates round-robin
   // and a segment's slot is its rank among the non-empty ones, found with a block-wide count
@@ -113,8 +126,8 @@ __global__ void __launch_bounds__(kPermThreads)
     } else {
       // more segment boundaries in one tile than the table holds (thousands of one-element
       // segments): every element searches the global offsets itself
-      int64_t seg = segment_of<OffT>(out_offsets, num_segments, i);
-      // skip back over empty segments that share the start
+      // (the last segment that starts at or before i is the non-empty one that holds it)
+      const int64_t seg = segment_of<OffT>(out_offsets, num_segments, i);
       src = load_off<OffT>(in_offsets, static_cast<int64_t>(perm[seg])) + (i - load_off<OffT>(out_offsets, seg));
     }
     out[i] = in[src];
