@@ -14,7 +14,7 @@ namespace b200tbe {
 namespace {
 
 constexpr int kPermThreads = 256;
-constexpr int kPermItems = 8;                       // elements per thread
+constexpr int kPermItems = 16;                       // elements per thread
 constexpr int kPermTile = kPermThreads * kPermItems;
 constexpr int kPermMaxSegs = 2048;                  // segment boundaries a tile keeps in shared memory
 
