@@ -24,7 +24,7 @@ namespace {
 
 constexpr int kBwdWarps = 8;
 constexpr int kBwdThreads = kBwdWarps * 32;
-constexpr int kLongRun = 512;           // lookups per chunk of a long run
+constexpr int kLongRun = 256;           // lookups per chunk of a long run
 constexpr int kSegThreads = 1024;
 constexpr int kSegItems = 4;
 constexpr int kSegTile = kSegThreads * kSegItems;
