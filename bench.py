@@ -29,6 +29,13 @@ if ROOT not in sys.path:
 from torchlib_xpu_b200 import cabi, workloads  # noqa: E402
 
 L2_FLUSH_BYTES = 512 << 20
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) of ONE table of the bench step -- 4 M fp16
+# rows x D=128, B=65536, about 1.67 M lookups -- from the ncu capture summarised in
+# profiles/tbe_step_one_table_traffic.md. Tables are processed one after another, each with its own
+# rows, ids and gradient columns, so a step of T tables moves T times this.
+FWD_TRAFFIC_PER_TABLE = None
+BWD_TRAFFIC_PER_TABLE = None
+TRAFFIC_NOTE = ("one-table ncu capture x tables (profiles/tbe_step_one_table_traffic.md)")
 TABLES_OVERRIDE = None   # --tables: fewer tables for --only runs (small profiler captures)
 
 
@@ -120,9 +127,11 @@ def uniform_half_table(num_elems, lo, hi, gen):
     return w
 
 
-def backward_launches(bits: int) -> int:
-    passes = (bits + 9) // 10
-    return 1 + passes * 5 + 3 + 3  # linearize, per pass hist+3 scan+scatter, segmentation, reduce
+def backward_launches(row_bits: int) -> int:
+    """Kernels one b200tbe_backward call launches for rows of at most 512 elements: two plan kernels,
+    linearize, per sort pass (11 bits each) histogram + 3 scan kernels + scatter, sweep, finish."""
+    passes = (row_bits + 10) // 11
+    return 2 + 1 + passes * 5 + 2
 
 
 def time_launches(fn, iters, flush=None):
@@ -171,7 +180,7 @@ class ShardedTbeStep:
         # pooled rows and their gradients travel as fp16
         self.pooled = torch.empty((B, self.total_D), dtype=torch.float16, device="cuda")
         self.grad = (torch.randn((B, self.total_D), device="cuda", generator=gen)).half()
-        need = cabi.backward_scratch_bytes(self.N, self.bits, D)
+        need = cabi.backward_scratch_bytes(self.N, self.bits, D, T)
         self.scratch = torch.empty(need, dtype=torch.uint8, device="cuda")
         # distinct rows touched (for the compulsory-byte count)
         table_of = torch.repeat_interleave(
@@ -199,7 +208,7 @@ class ShardedTbeStep:
         cabi.backward(self.weights, self.weights_offsets, self.D_offsets, self.hash_size_cumsum,
                       self.bits, self.D, self.indices, self.offsets, self.B, grad,
                       cabi.OPT_ROWWISE_ADAGRAD, 0.01, 1e-8, self.momentum, self.momentum_offsets,
-                      scratch=self.scratch, grad_ready_event=ready)
+                      scratch=self.scratch, grad_ready_event=ready, max_table_rows=self.E)
 
     def result(self):
         """Pooled rows this rank ends the forward with (its batch slice, all tables, when sharded)."""
@@ -211,7 +220,7 @@ class ShardedTbeStep:
 
     def launches_per_step(self):
         extra = 0 if self.exchange is None else self.exchange.launches_per_step()
-        return 1 + backward_launches(self.bits) + extra
+        return 1 + backward_launches(max(1, (self.E - 1).bit_length())) + extra
 
     def fwd_bytes(self):
         return workloads.forward_bytes(self.N, self.U, self.D * 2, self.T, self.B, self.D, 2)
@@ -224,8 +233,12 @@ class ShardedTbeStep:
 # CPU arm: FBGEMM-core forward + the C oracle's backward on a bounded sample of the same workload
 # --------------------------------------------------------------------------------------------
 def cpu_sample_rate(cfg, budget_s=12.0):
+    """One table of the bench step at the full batch (so that the share of repeated rows is the
+    step's own), forward by FBGEMM-core + backward/Adagrad by the C oracle, on every core this
+    process may run on -- set explicitly: launchers export OMP_NUM_THREADS=1."""
     import oracle
-    T, E, D, B = 2, cfg["E"], cfg["D"], 8192
+    T, E, D, B = 1, cfg["E"], cfg["D"], cfg["B"]
+    threads = oracle.set_num_threads(len(os.sched_getaffinity(0)))
     inp = workloads.tbe_inputs(T, B, E, D, cfg["L_lo"], cfg["L_hi"], cfg["seed"], "zipf", cfg["alpha"])
     g = torch.Generator().manual_seed(7)
     W = ((torch.rand(T * E * D, generator=g) * 0.02) - 0.01).half().numpy()
@@ -235,7 +248,6 @@ def cpu_sample_rate(cfg, budget_s=12.0):
     grad = torch.randn((B, T * D), generator=g).numpy()
     mom = np.zeros(T * E, dtype=np.float32)
     rows = [E] * T
-    threads = oracle.num_threads()
     t0, reps = time.perf_counter(), 0
     while True:
         oracle.tbe_forward(W, oracle.FP16, wo, Do, B, inp.indices, inp.offsets, backend="ref",
@@ -243,11 +255,12 @@ def cpu_sample_rate(cfg, budget_s=12.0):
         oracle.tbe_backward(W, oracle.FP16, wo, Do, hs, B, inp.indices, inp.offsets, grad, mom, hs[:-1],
                             oracle.ROWWISE_ADAGRAD, 0.01, 1e-8)
         reps += 1
-        if time.perf_counter() - t0 > budget_s or reps >= 200:
+        if time.perf_counter() - t0 > budget_s or reps >= 400:
             break
     dt = time.perf_counter() - t0
     sample = ("%d reps of fwd (FBGEMM-core EmbeddingSpMDM, torch-bundled) + bwd/Adagrad (C oracle) on "
-              "T=%d E=%d D=%d fp16 B=%d, %d lookups each, %.1f s" % (reps, T, E, D, B, inp.num_lookups, dt))
+              "one table of the step: E=%d D=%d fp16, B=%d, %d lookups each, %d threads, %.1f s"
+              % (reps, E, D, B, inp.num_lookups, threads, dt))
     return inp.num_lookups * reps / dt, threads, sample, dt / reps
 
 
@@ -357,18 +370,18 @@ def _bench_train(entry, flush, gen, iters):
     out = torch.empty((B, T * D), device="cuda")
     grad = torch.randn((B, T * D), device="cuda", generator=gen)
     bits = (T * E - 1).bit_length()
-    scratch = torch.empty(cabi.backward_scratch_bytes(inp.num_lookups, bits, D), dtype=torch.uint8, device="cuda")
+    scratch = torch.empty(cabi.backward_scratch_bytes(inp.num_lookups, bits, D, T), dtype=torch.uint8, device="cuda")
     fwd = lambda: cabi.forward(W, wo, Do, T * D, D, idx, offs, B, outputs=[out], output_stride=T * D,
                                rows_per_dest=B)
     bwd = lambda: cabi.backward(W, wo, Do, hs, bits, D, idx, offs, B, grad, cabi.OPT_ROWWISE_ADAGRAD, 0.01,
-                                1e-8, mom, hs[:-1], scratch=scratch)
+                                1e-8, mom, hs[:-1], scratch=scratch, max_table_rows=E)
     fwd(); bwd()
     ms, _ = time_launches(fwd, iters, flush)
     entry("tbe_fp16_forward(config3)", workloads.forward_bytes(inp.num_lookups, U, D * 2, T, B, D, 4), ms,
           inp.num_lookups, {"unique_rows": U})
     ms, _ = time_launches(bwd, iters, flush)
     entry("tbe_fp16_backward_adagrad(config3)", workloads.backward_bytes(inp.num_lookups, U, D * 2, T, B, D, 4),
-          ms, inp.num_lookups, {"kernels_per_call": backward_launches(bits)})
+          ms, inp.num_lookups, {"kernels_per_call": backward_launches((E - 1).bit_length())})
 
 
 def _bench_permute(entry, flush, gen, iters):
@@ -448,6 +461,169 @@ def _bench_nbit(entry, flush, gen, iters):
     entry("tbe_nbit_forward(config4)", bytes_, ms, inp.num_lookups, {"unique_rows": int(sum(U_by_table))})
 
 
+# --------------------------------------------------------------------------------------------
+# Parity of the bench step itself (sampled, against the CPU oracle) and of the exchange (bitwise,
+# against NCCL's all-to-all). Runs once before the timed region; a mismatch ends the run.
+# --------------------------------------------------------------------------------------------
+def parity_checks(step, dist):
+    import oracle
+    from tests import sampled_parity
+
+    T, E, D, B = step.T, step.E, step.D, step.B
+    tables = sorted({0, T // 3, (2 * T) // 3, T - 1})
+    checks = {}
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    rows = torch.full((T,), E, dtype=torch.int64, device="cuda")
+    # the lookup of this rank's tables for the whole batch, as a local matrix
+    pooled = cabi.forward(step.weights, step.weights_offsets, step.D_offsets, step.total_D, D, step.indices,
+                          step.offsets, B, output_dtype=torch.float16, rows_per_table=rows, status=status)
+    n_bags = 0
+    for t in tables:
+        g = torch.Generator().manual_seed(900 + t)
+        bags = torch.sort(torch.randperm(B, generator=g)[:64]).values
+        # fp16 pooled rows: the north-star tolerance plus the rounding of the stored value
+        n_bags += sampled_parity.forward_sample_check(step.weights, D, t * E * D, t * D, D, oracle.FP16,
+                                                      step.indices, step.offsets, B, t, pooled, bags, 2e-3, 1e-3)
+    checks["forward_vs_oracle"] = "ok: %d sampled bags of tables %s" % (n_bags, tables)
+    if step.exchange is not None:
+        from torchlib_xpu_b200 import sharded
+        step.forward()                                   # the fused lookup + peer stores + barrier
+        ref = sharded.reference_exchange(pooled)         # NCCL all_to_all_single of the local matrix
+        torch.cuda.synchronize()
+        if not torch.equal(ref, step.exchange.recv):
+            raise SystemExit("parity: the fused exchange differs from the all-to-all of the local lookups")
+        checks["exchange_vs_all_to_all"] = "ok: bitwise, %d x %d" % tuple(ref.shape)
+        del ref
+    del pooled
+    samples = [sampled_parity.BackwardSample(step.weights, t * E * D, D, oracle.FP16, step.momentum, t * E,
+                                             step.indices, step.offsets, B, t, hot=16, extra=240, seed=t)
+               for t in tables]
+    if step.exchange is not None:
+        from torchlib_xpu_b200 import sharded
+        want = sharded.reference_gradient_exchange(step.exchange.grad_slice)
+    step.backward()
+    torch.cuda.synchronize()
+    grad = step.grad if step.exchange is None else step.exchange.grad_local
+    if step.exchange is not None:
+        if not torch.equal(want, grad):
+            raise SystemExit("parity: the gradient push differs from the all-to-all of the gradient slices")
+        checks["gradient_push_vs_all_to_all"] = "ok: bitwise, %d x %d" % tuple(want.shape)
+        del want
+    n_rows = 0
+    for t, smp in zip(tables, samples):
+        n_rows += smp.check(step.weights, step.momentum, grad, t * D, oracle.ROWWISE_ADAGRAD, 0.01, 1e-8)
+    checks["backward_vs_oracle"] = ("ok: %d sampled rows (16 hottest + 240 touched per table), longest run %d "
+                                    "lookups" % (n_rows, max(smp.max_run for smp in samples)))
+    if int(status.item()) != 0:
+        raise SystemExit("parity: device status %d" % int(status.item()))
+    if dist is not None:
+        flag = torch.ones(1, device="cuda")
+        dist.all_reduce(flag)                            # every rank got here
+        checks["ranks_checked"] = int(flag.item())
+    return checks
+
+
+# --------------------------------------------------------------------------------------------
+# End to end: the loop a trainer with host-side batches runs. Ids, offsets and gradients come from
+# pinned host memory every step and the pooled rows go back to the host every step; the copies run
+# on side streams (the next step's ids while this step computes, the gradients under the forward,
+# the result under the backward) and every one of them is inside the timed region.
+# One GPU: through the operator library, torch.ops.fbgemm.split_embedding_codegen_lookup_rowwise_
+# adagrad_function and autograd's backward (the plugin call a user makes). Sharded: the lookup that
+# scatters into the peers' buffers has no fbgemm operator, so the step stays on the C ABI.
+# --------------------------------------------------------------------------------------------
+def end_to_end(step, dist, world, args, lookups_all, idx_dtype, barrier):
+    T, E, D, B = step.T, step.E, step.D, step.B
+    h_idx = step.indices.to(idx_dtype).cpu().pin_memory()
+    h_off = step.offsets.to(idx_dtype).cpu().pin_memory()
+    grad_in = step.grad if step.exchange is None else step.exchange.grad_slice
+    h_grad = grad_in.cpu().pin_memory()
+    h_out = torch.empty(step.result().shape, dtype=step.result().dtype).pin_memory()
+    # whole-job bytes: every rank copies its own inputs and its own slice of the result
+    h2d = (h_idx.numel() * h_idx.element_size() + h_off.numel() * h_off.element_size() +
+           h_grad.numel() * h_grad.element_size()) * world
+    d2h = h_out.numel() * h_out.element_size() * world
+    main = torch.cuda.current_stream()
+    copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+    idx_bufs = [torch.empty(step.N, dtype=idx_dtype, device="cuda") for _ in range(2)]
+    off_bufs = [torch.empty(T * B + 1, dtype=idx_dtype, device="cuda") for _ in range(2)]
+    keep = (step.indices, step.offsets)
+    pipe = {"k": 0, "bwd_done": None, "out_done": None}
+    module = None
+    if step.exchange is None:
+        from torchlib_xpu_b200 import tbe_modules as tm
+        module = tm.SplitTableBatchedEmbeddingBagsCodegen(
+            [(E, D)] * T, tm.OptimType.EXACT_ROWWISE_ADAGRAD, 0.01, 1e-8, tm.PoolingMode.SUM,
+            tm.SparseType.FP16, tm.SparseType.FP16, weights_dev=step.weights, momentum1_dev=step.momentum)
+
+    def e2e_step():
+        k = pipe["k"]
+        pipe["k"] = k + 1
+        idx, off = idx_bufs[k & 1], off_bufs[k & 1]
+        in_ready, grad_ready = torch.cuda.Event(), torch.cuda.Event()
+        fwd_done, out_done, bwd_done = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
+        with torch.cuda.stream(copy_in):
+            # this id buffer was last read by the backward two steps back, which the gradient
+            # copy of the previous step already waited for
+            idx.copy_(h_idx, non_blocking=True)
+            off.copy_(h_off, non_blocking=True)
+            in_ready.record(copy_in)
+            if pipe["bwd_done"] is not None:
+                copy_in.wait_event(pipe["bwd_done"])   # the previous backward reads the gradient buffer
+            grad_in.copy_(h_grad, non_blocking=True)
+            grad_ready.record(copy_in)
+        main.wait_event(in_ready)
+        if module is not None:
+            pooled = module(idx, off)                  # torch.ops.fbgemm.* forward: allocates its result
+            fwd_done.record(main)
+            with torch.cuda.stream(copy_out):
+                copy_out.wait_event(fwd_done)
+                h_out.copy_(pooled, non_blocking=True)
+                out_done.record(copy_out)
+            pooled.record_stream(copy_out)
+            main.wait_event(grad_ready)
+            pooled.backward(grad_in)                   # the fused backward + Adagrad, through autograd
+        else:
+            step.indices, step.offsets = idx, off
+            step.forward()
+            fwd_done.record(main)
+            with torch.cuda.stream(copy_out):
+                copy_out.wait_event(fwd_done)
+                h_out.copy_(step.result(), non_blocking=True)
+                out_done.record(copy_out)
+            main.wait_event(grad_ready)
+            # peers write the next forward's rows into this rank's result buffer: the copy-out has
+            # to be over before the barrier inside the backward's gradient exchange
+            main.wait_event(out_done)
+            step.backward()
+        bwd_done.record(main)
+        pipe["bwd_done"], pipe["out_done"] = bwd_done, out_done
+
+    e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_steps = max(2, min(args.steps, 10))
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    main.wait_event(pipe["out_done"])   # the last result has to be on the host inside the timed region
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if dist is not None:
+        t = torch.tensor([e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    step.indices, step.offsets = keep
+    return {"value": lookups_all / (e2e_ms / e2e_steps / 1e3), "unit": "lookups/s",
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / e2e_steps,
+            "steps": e2e_steps, "ids": str(idx_dtype).replace("torch.", ""),
+            "through": ("torch.ops.fbgemm.split_embedding_codegen_lookup_rowwise_adagrad_function + autograd "
+                        "(libb200tbe_torch_ops.so)" if module is not None else
+                        "b200tbe_forward / b200tbe_exchange_push / b200tbe_backward (C ABI; the sharded lookup "
+                        "has no fbgemm operator)")}
+
+
 def _claim_stdout():
     """Libraries (NCCL among them) print banners on stdout; the contract is ONE JSON line there. Point
     fd 1 at stderr for the run and hand back a file on the original stdout for the final line."""
@@ -501,11 +677,17 @@ def main():
         return
 
     step = ShardedTbeStep(rank, world, cfg, small=args.small)
+    if args.tables is not None:
+        raise SystemExit("--tables goes with --only")
 
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
+
+    # ---- parity of this very workload, before anything is timed -----------------------------
+    checks = parity_checks(step, dist)
+    barrier()
 
     for _ in range(args.warmup):
         step.step()
@@ -514,7 +696,6 @@ def main():
     # ---- device-resident timing: exactly K steps between barriers -------------------------
     sampler = ClockSampler(local_rank)
     sampler.start()
-    ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
     fwd_ms, bwd_ms = [], []
     barrier()
     t_start = torch.cuda.Event(enable_timing=True)
@@ -547,78 +728,38 @@ def main():
     ms_per_step = total_ms / args.steps
     value = lookups_all / (ms_per_step / 1e3)
 
-    # ---- end to end: host buffers in, pooled rows out, every step ---------------------------
-    h_idx = step.indices.cpu().pin_memory()
-    h_off = step.offsets.cpu().pin_memory()
-    grad_in = step.grad if step.exchange is None else step.exchange.grad_slice
-    h_grad = grad_in.cpu().pin_memory()
-    h_out = torch.empty(step.result().shape, dtype=step.result().dtype).pin_memory()
-    # whole-job bytes: every rank copies its own inputs and its own slice of the result
-    h2d = (h_idx.numel() * 8 + h_off.numel() * 8 + h_grad.numel() * h_grad.element_size()) * world
-    d2h = h_out.numel() * h_out.element_size() * world
-
-    # The loop a trainer with host-side batches runs: the next step's ids are copied in while the
-    # current step computes (two id buffers), the gradient copy overlaps the forward, the result
-    # copy overlaps the backward. Every step's copies are inside the timed region.
-    main = torch.cuda.current_stream()
-    copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
-    idx_bufs = [step.indices, torch.empty_like(step.indices)]
-    off_bufs = [step.offsets, torch.empty_like(step.offsets)]
-    pipe = {"k": 0, "bwd_done": None, "out_done": None}
-
-    def e2e_step():
-        k = pipe["k"]
-        pipe["k"] = k + 1
-        idx, off = idx_bufs[k & 1], off_bufs[k & 1]
-        in_ready, grad_ready = torch.cuda.Event(), torch.cuda.Event()
-        fwd_done, out_done, bwd_done = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
-        with torch.cuda.stream(copy_in):
-            # this id buffer was last read by the backward two steps back, which the gradient
-            # copy of the previous step already waited for
-            idx.copy_(h_idx, non_blocking=True)
-            off.copy_(h_off, non_blocking=True)
-            in_ready.record(copy_in)
-            if pipe["bwd_done"] is not None:
-                copy_in.wait_event(pipe["bwd_done"])   # the previous backward reads the gradient buffer
-            grad_in.copy_(h_grad, non_blocking=True)
-            grad_ready.record(copy_in)
-        step.indices, step.offsets = idx, off
-        main.wait_event(in_ready)
-        if world == 1 and pipe["out_done"] is not None:
-            main.wait_event(pipe["out_done"])          # the result buffer is still being copied out
-        step.forward()
-        fwd_done.record(main)
-        with torch.cuda.stream(copy_out):
-            copy_out.wait_event(fwd_done)
-            h_out.copy_(step.result(), non_blocking=True)
-            out_done.record(copy_out)
-        main.wait_event(grad_ready)
-        if world > 1:
-            # peers write the next forward's rows into this rank's result buffer: the copy-out has
-            # to be over before the barrier inside the backward's gradient exchange
-            main.wait_event(out_done)
-        step.backward()
-        bwd_done.record(main)
-        pipe["bwd_done"], pipe["out_done"] = bwd_done, out_done
-
-    e2e_step()
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e2e_steps = max(2, min(args.steps, 10))
-    e0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    main.wait_event(pipe["out_done"])   # the last result has to be on the host inside the timed region
-    e1.record()
-    barrier()
-    e2e_ms = e0.elapsed_time(e1)
-    if dist is not None:
-        t = torch.tensor([e2e_ms], device="cuda", dtype=torch.float64)
+    # ---- the gradient push alone (N > 1): bytes that cross NVLink / device time ---------------
+    nvlink = None
+    if step.exchange is not None:
+        ex = step.exchange
+        times = []
+        for _ in range(5):
+            barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            ex.push_gradients()
+            b.record()
+            b.synchronize()
+            times.append(a.elapsed_time(b))
+            ex.barrier()
+        push_ms = float(np.median(times))
+        t = torch.tensor([push_ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
-    e2e_value = lookups_all / (e2e_ms / e2e_steps / 1e3)
-    step.indices, step.offsets = idx_bufs[0], off_bufs[0]
-    del h_idx, h_off, h_grad, h_out, idx_bufs, off_bufs
+        push_ms = float(t.item())
+        out_bytes = ex.grad_slice.numel() * ex.grad_slice.element_size() * (world - 1) // world
+        nvlink = {"bound": "nvlink", "kernel": "exchange_push_kernel (gradient blocks to their owners)",
+                  "bytes_out_per_rank": out_bytes, "ms": push_ms, "achieved": out_bytes / push_ms / 1e6,
+                  "peak": 770.0, "unit": "GB/s", "frac": out_bytes / push_ms / 1e6 / 770.0,
+                  "peak_kind": "of the peer-copy bandwidth measured on this pool (770 GB/s per direction; "
+                               "900 nominal)",
+                  "forward_note": "the pooled rows cross NVLink inside the lookup kernel (same bytes the "
+                                  "other way); phases_ms.forward includes them"}
+
+    # ---- end to end: host buffers in, pooled rows out, every step ---------------------------
+    e2e = {}
+    for label, idx_dtype in (("int64_ids", torch.int64), ("int32_ids", torch.int32)):
+        e2e[label] = end_to_end(step, dist, world, args, lookups_all, idx_dtype, barrier)
+    torch.cuda.empty_cache()
 
     line = {
         "metric": "TBE pooled-row lookups/s (fwd + bwd with fused row-wise Adagrad)",
@@ -634,8 +775,9 @@ def main():
             "exchange": "none (1 GPU)" if world == 1 else step.exchange.describe(),
         },
         "clocks": clocks,
-        "e2e": {"value": e2e_value, "unit": "lookups/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / e2e_steps},
+        "e2e": e2e["int64_ids"],
+        "e2e_int32_ids": e2e["int32_ids"],
+        "checks": checks,
         "gpu_launches": step.launches_per_step() * args.steps,
         "phases_ms": {"forward": fwd_avg, "backward": bwd_avg},
     }
@@ -645,14 +787,18 @@ def main():
     line["roofline"] = {
         "bound": "hbm", "kernel": "b200tbe_backward (linearize + radix sort + segment + reduce/update)",
         "achieved": bwd_bytes / bwd_avg / 1e6, "peak": peak_gbs, "unit": "GB/s",
-        "frac": bwd_bytes / bwd_avg / 1e6 / peak_gbs, "traffic": None, "peak_kind": "of " + peak_kind,
-        "algorithmic_bytes": bwd_bytes,
+        "frac": bwd_bytes / bwd_avg / 1e6 / peak_gbs,
+        "traffic": None if BWD_TRAFFIC_PER_TABLE is None else BWD_TRAFFIC_PER_TABLE * step.T,
+        "traffic_note": TRAFFIC_NOTE, "peak_kind": "of " + peak_kind, "algorithmic_bytes": bwd_bytes,
     }
     line["roofline_forward"] = {
         "bound": "hbm", "kernel": "tbe_forward_bags_kernel", "achieved": fwd_bytes / fwd_avg / 1e6,
         "peak": peak_gbs, "unit": "GB/s", "frac": fwd_bytes / fwd_avg / 1e6 / peak_gbs,
-        "traffic": None, "peak_kind": "of " + peak_kind, "algorithmic_bytes": fwd_bytes,
+        "traffic": None if FWD_TRAFFIC_PER_TABLE is None else FWD_TRAFFIC_PER_TABLE * step.T,
+        "traffic_note": TRAFFIC_NOTE, "peak_kind": "of " + peak_kind, "algorithmic_bytes": fwd_bytes,
     }
+    if nvlink is not None:
+        line["roofline_nvlink"] = nvlink
 
     if rank == 0 and world == 1:
         del step

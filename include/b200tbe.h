@@ -149,12 +149,11 @@ B200TBE_API int b200tbe_nbit_forward(const b200tbe_nbit_forward_params* p, b200t
  * TBE backward with the optimizer applied in place (the backward half of
  * torch.ops.fbgemm.split_embedding_codegen_lookup_{sgd,rowwise_adagrad}_function).
  *
- * Steps, all on `stream`: (1) every lookup gets the key hash_size_cumsum[t] + index and its bag id
- * as payload; (2) a least-significant-digit radix sort over total_hash_size_bits key bits; (3)
- * run-length segmentation of the sorted keys; (4) one warp per distinct row sums the gradient
- * slices of its lookups (a segment longer than a fixed chunk is first reduced chunk-wise by many
- * warps, then combined in a fixed order, so results do not depend on scheduling); (5) the row is
- * updated once ("exact" semantics):
+ * Steps, all on `stream`: (1) every lookup gets its row id as key and its bag id as payload; (2) a
+ * least-significant-digit radix sort of every table's lookups by row id; (3) groups of lanes walk
+ * the sorted lookups, summing the gradient slices of each run of equal rows (a run that spans
+ * several walks is first reduced piecewise, then combined in a fixed order, so results do not
+ * depend on scheduling); (4) the row is updated once ("exact" semantics):
  *   SGD:              w -= lr * g
  *   row-wise Adagrad: m += mean_d(g_d^2);  w -= lr / (sqrt(m) + eps) * g
  * g is the summed gradient (divided by the bag length first when pooling_mode is MEAN, multiplied
@@ -196,12 +195,17 @@ typedef struct {
                                        first kernel that reads grad_output, so a gradient exchange
                                        running on another stream overlaps the part of the backward
                                        that needs only the indices. */
+  int64_t max_table_rows;           /* optional: rows of the largest table (0: unknown). The sort then
+                                       covers only the bits of a row id inside one table instead of
+                                       total_hash_size_bits; a table with more rows than this is
+                                       flagged B200TBE_DEV_UNSUPPORTED_SHAPE and its excess rows are
+                                       treated as out of range. */
 } b200tbe_backward_params;
 
-/* Scratch needed by b200tbe_backward for num_indices lookups with keys of total_hash_size_bits
- * bits and rows of at most max_D elements. */
+/* Scratch needed by b200tbe_backward for num_indices lookups in T tables with keys of
+ * total_hash_size_bits bits and rows of at most max_D elements. */
 B200TBE_API size_t b200tbe_backward_scratch_bytes(int64_t num_indices, int32_t total_hash_size_bits,
-                                                  int32_t max_D);
+                                                  int32_t max_D, int32_t T);
 B200TBE_API int b200tbe_backward(const b200tbe_backward_params* p, b200tbe_stream_t stream);
 
 /* The sort of step (2) on its own: keys_in/vals_in are sorted by the low `key_bits` bits into
@@ -213,6 +217,20 @@ B200TBE_API int b200tbe_radix_sort_pairs(void* keys_in, uint32_t* vals_in, void*
                                          uint32_t* vals_out, int64_t n, int32_t key_bytes,
                                          int32_t key_bits, void* scratch, size_t scratch_bytes,
                                          b200tbe_stream_t stream);
+
+/* Segmented form: the n pairs are num_segments independent segments, segment s being positions
+ * [seg_offsets[s], seg_offsets[s+1]) (device array of num_segments + 1 int32 or int64 values,
+ * non-decreasing, last = n); every segment is sorted on its own, stable, by the low key_bits bits of
+ * its 4-byte keys, and no pair leaves its segment. This is step (2) of b200tbe_backward, where a
+ * segment is one table's lookups and the key a row id: the passes cover the bits of a row id only,
+ * not those that tell tables apart. The plan (segments -> tiles) is built on the device; the host
+ * never reads seg_offsets. Arrays as b200tbe_radix_sort_pairs. */
+B200TBE_API size_t b200tbe_radix_sort_segments_scratch_bytes(int64_t n, int32_t num_segments);
+B200TBE_API int b200tbe_radix_sort_segments(uint32_t* keys_in, uint32_t* vals_in, uint32_t* keys_out,
+                                            uint32_t* vals_out, int64_t n, const void* seg_offsets,
+                                            int32_t offset_bytes, int32_t num_segments,
+                                            int32_t key_bits, void* scratch, size_t scratch_bytes,
+                                            b200tbe_stream_t stream);
 
 /* The same sort for callers that cannot allocate device memory when they call it -- a plain C or
  * C++ host with no tensor allocator to borrow scratch from, a server that has already given all of
@@ -268,33 +286,14 @@ B200TBE_API int b200tbe_nv12_to_rgb(const uint8_t* y_plane, const uint8_t* uv_pl
 /* ------------------------------------------------------------------------------------------------
  * Gradient exchange of the table-wise-sharded configuration (the step a sharded caller runs between
  * its dense part and b200tbe_backward; the pooled rows travel the other way inside b200tbe_forward,
- * which can scatter into peer-mapped destination buffers). Source s is a peer's gradient matrix
- * with rows src_stride_bytes apart; the row block [src_col_offset_bytes, +row_bytes) of its rows
- * [0, rows_per_src) lands in rows [s*rows_per_src, (s+1)*rows_per_src) of dst. All byte counts and
- * pointers must be multiples of 16. The kernel only reads the sources; making sure they are
- * complete before, and not overwritten during, the call is the caller's job.
+ * which can scatter into peer-mapped destination buffers), as a push, which is what NVLink prefers
+ * (stores stream, loads wait): src is this rank's gradient matrix, rows x (num_dsts * block_bytes)
+ * with rows src_stride_bytes apart; column block d of row r is stored at row dst_row_offset + r of
+ * destination d's matrix (rows dst_stride_bytes apart, block_bytes wide; peer-mapped or local). Byte
+ * counts and pointers are multiples of 16. The caller orders the call after the destinations'
+ * previous readers and orders the destinations' next readers after it (stream-ordered barriers). No
+ * counterpart in the reference.
  * ---------------------------------------------------------------------------------------------- */
-typedef struct {
-  const void* srcs[B200TBE_MAX_DESTS]; /* one per source rank, peer-mapped or local */
-  void* dst;
-  int64_t src_stride_bytes;
-  int64_t src_col_offset_bytes;
-  int64_t dst_stride_bytes;
-  int64_t rows_per_src;
-  int64_t row_bytes;
-  int32_t num_srcs;
-} b200tbe_exchange_pull_params;
-
-B200TBE_API int b200tbe_exchange_pull(const b200tbe_exchange_pull_params* p,
-                                      b200tbe_stream_t stream);
-
-/* The same exchange as a push, which is what NVLink prefers (stores stream, loads wait): src is this
- * rank's gradient matrix, rows x (num_dsts * block_bytes) with rows src_stride_bytes apart; column
- * block d of row r is stored at row dst_row_offset + r of destination d's matrix (rows
- * dst_stride_bytes apart, block_bytes wide; peer-mapped or local). Byte counts and pointers are
- * multiples of 16. The caller orders the call after the destinations' previous readers and orders
- * the destinations' next readers after it (stream-ordered barriers). No counterpart in the
- * reference, like the pull. */
 typedef struct {
   const void* src;
   void* dsts[B200TBE_MAX_DESTS];

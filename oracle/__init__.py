@@ -247,8 +247,29 @@ def jagged_dense_elementwise_add(x_values, offsets_list, y):
     return out
 
 
+def permute_segments(values, lengths, perm):
+    """out segment j = in segment perm[j] (numpy): the data movement of
+    torch.ops.fbgemm.permute_2D_sparse_data, restated as an index gather."""
+    values, lengths, perm = np.asarray(values), np.asarray(lengths, dtype=np.int64), np.asarray(perm, dtype=np.int64)
+    in_off = np.zeros(lengths.size + 1, dtype=np.int64)
+    np.cumsum(lengths, out=in_off[1:])
+    out_len = lengths[perm]
+    out_off = np.zeros(perm.size + 1, dtype=np.int64)
+    np.cumsum(out_len, out=out_off[1:])
+    src = np.arange(int(out_off[-1]), dtype=np.int64) + np.repeat(in_off[:-1][perm] - out_off[:-1], out_len)
+    return values[src]
+
+
 def num_threads() -> int:
     return int(ref_lib().ref_num_threads())
+
+
+def set_num_threads(n: int) -> int:
+    """Thread count of both oracle libraries from here on (they share one OpenMP runtime), whatever
+    OMP_NUM_THREADS the launcher exported. Returns the count in effect."""
+    c_lib()
+    ref_lib().ref_set_num_threads(ctypes.c_int(int(n)))
+    return num_threads()
 
 
 # ---- NV12 -> RGB24 (nv12_oracle.c) ----------------------------------------------------------

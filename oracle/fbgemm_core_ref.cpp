@@ -64,6 +64,13 @@ bool run_block(const Kernel& kernel, const InType* table, int64_t data_size, int
 
 REF_API int ref_num_threads() { return omp_get_max_threads(); }
 
+// The OpenMP runtime is shared by the oracle libraries of the process, so this sets the thread count
+// of the C restatement too. Launchers such as torchrun export OMP_NUM_THREADS=1; a timed CPU arm
+// states its thread count itself instead of inheriting that.
+REF_API void ref_set_num_threads(int n) {
+  if (n >= 1) omp_set_num_threads(n);
+}
+
 // fp32 / fp16 tables; out fp32 [B, out_stride]. rows_per_table bounds the indices (FBGEMM checks).
 REF_API int ref_tbe_forward(const void* dev_weights, int weights_ty, const int64_t* weights_offsets,
                             const int32_t* D_offsets, const int64_t* rows_per_table, int T, int B,

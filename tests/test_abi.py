@@ -51,4 +51,4 @@ def test_argument_validation_needs_no_gpu():
     assert lib.b200tbe_dense_to_jagged(ctypes.byref(s), None, None, None) == -4
     assert lib.b200tbe_radix_sort_pairs(None, None, None, None, -1, 4, 8, None, 0, None) == -1
     assert lib.b200tbe_radix_sort_scratch_bytes(0) >= 0
-    assert lib.b200tbe_backward_scratch_bytes(1 << 20, 25, 128) > (1 << 20) * 8
+    assert lib.b200tbe_backward_scratch_bytes(1 << 20, 25, 128, 8) > (1 << 20) * 8

@@ -50,6 +50,35 @@ def test_radix_sort_ignores_high_bits():
     assert np.array_equal(vs.cpu().numpy(), vals[order])
 
 
+@pytest.mark.parametrize("sizes,bits", [
+    ([0, 5, 0, 4096, 4097, 1], 9), ([10_000, 300, 256, 257, 8192], 3), ([20_000, 9_000], 22),
+    ([255, 256, 512, 1], 1), ([70_000], 11), ([3_000, 0, 0, 12_000, 0], 17), ([1] * 300, 5),
+    ([150_000, 2, 90_000], 32),
+])
+@pytest.mark.parametrize("off_dtype", [np.int64, np.int32])
+def test_segmented_sort_sorts_every_segment_on_its_own(sizes, bits, off_dtype):
+    """b200tbe_radix_sort_segments (the backward's sort): every segment is stably sorted by the low
+    bits of its keys, pairs never leave their segment; empty segments, segments that end inside a
+    tile, one key per segment."""
+    rng = workloads.rng_for(500 + len(sizes) + bits)
+    n = int(sum(sizes))
+    seg = np.zeros(len(sizes) + 1, dtype=np.int64)
+    np.cumsum(sizes, out=seg[1:])
+    keys = rng.integers(0, 1 << 32, size=n, dtype=np.uint64).astype(np.uint32)
+    if n > 1000:
+        keys[rng.random(n) < 0.4] = keys[0]
+    vals = np.arange(n, dtype=np.int32)
+    ks, vs = cabi.radix_sort_segments(_dev(keys.view(np.int32)), _dev(vals), _dev(seg.astype(off_dtype)), bits)
+    torch.cuda.synchronize()
+    want_k, want_v = np.empty_like(keys), np.empty_like(vals)
+    mask = np.uint32((1 << bits) - 1) if bits < 32 else np.uint32(0xffffffff)
+    for a, b in zip(seg[:-1], seg[1:]):
+        order = np.argsort(keys[a:b] & mask, kind="stable")
+        want_k[a:b], want_v[a:b] = keys[a:b][order], vals[a:b][order]
+    assert np.array_equal(ks.cpu().numpy().view(np.uint32), want_k)
+    assert np.array_equal(vs.cpu().numpy(), want_v)
+
+
 def _backward_case(rng, rows, Ds, B, L_lo, L_hi, wdtype, gdtype, pooling, opt, weighted,
                    idx_dtype=np.int64, hot_row=None):
     T = len(Ds)
@@ -71,7 +100,7 @@ def _backward_case(rng, rows, Ds, B, L_lo, L_hi, wdtype, gdtype, pooling, opt, w
 
 
 def _check(T, W, wo, Do, offsets, indices, psw, grad, hs, mom, B, wdtype, gdtype, pooling, opt,
-           idx_dtype=np.int64, lr=0.05, eps=1e-8):
+           idx_dtype=np.int64, lr=0.05, eps=1e-8, rows_hint=True, update_rtol=None):
     ty = oracle.FP32 if wdtype == np.float32 else oracle.FP16
     W_ref, m_ref = W.copy(), mom.copy()
     oracle.tbe_backward(W_ref, ty, wo, Do, hs, B, indices, offsets, grad, m_ref, hs[:-1], opt, lr, eps,
@@ -83,11 +112,18 @@ def _check(T, W, wo, Do, offsets, indices, psw, grad, hs, mom, B, wdtype, gdtype
     cabi.backward(dW, _dev(wo), _dev(Do), _dev(hs), bits, int(np.max(np.diff(Do))),
                   _dev(indices.astype(idx_dtype)), _dev(offsets.astype(idx_dtype)), B, dgrad, opt, lr,
                   eps, dm, _dev(hs[:-1].copy()), pooling, None if psw is None else _dev(psw),
-                  status=status)
+                  status=status, max_table_rows=int(np.max(np.diff(hs))) if rows_hint else 0)
     torch.cuda.synchronize()
     assert int(status.item()) == 0
     got_W = dW.float().cpu().numpy()
     np.testing.assert_allclose(got_W, W_ref.astype(np.float32), rtol=RTOL, atol=ATOL)
+    if update_rtol is not None:
+        # the absolute tolerance above is loose against small weights: compare the UPDATES too
+        # (an fp16 row can only move in steps of its own spacing, hence the atol of two spacings)
+        old = W.astype(np.float32)
+        spacing = np.spacing(np.abs(W_ref).astype(np.float16)).astype(np.float32) if wdtype == np.float16 else 0.0
+        np.testing.assert_allclose(got_W - old, W_ref.astype(np.float32) - old, rtol=update_rtol,
+                                   atol=2 * np.max(spacing) + 1e-7)
     # rows that no lookup touched are bit-identical
     touched = np.zeros(int(hs[-1]), dtype=bool)
     for t in range(T):
@@ -125,6 +161,79 @@ def test_backward_long_runs_and_fp16_grads(gdtype):
     case = _backward_case(rng, rows, Ds, B, 5, 40, np.float16, gdtype, oracle.SUM,
                           oracle.ROWWISE_ADAGRAD, False, hot_row=17)
     _check(*case, B, np.float16, gdtype, oracle.SUM, oracle.ROWWISE_ADAGRAD, lr=0.01)
+
+
+@pytest.mark.parametrize("wdtype", [np.float32, np.float16])
+def test_backward_wide_rows_with_fp16_gradients(wdtype):
+    """Rows of 512 and 1024 elements with fp16 gradients (the 1024-element table runs on the ring
+    engine, whose lanes hold elements, not gradient bytes), one of them with a long run."""
+    rng = workloads.rng_for(444)
+    rows, Ds, B = [300, 64], [512, 1024], 400
+    case = _backward_case(rng, rows, Ds, B, 0, 12, wdtype, np.float16, oracle.SUM,
+                          oracle.ROWWISE_ADAGRAD, False, hot_row=5)
+    _check(*case, B, wdtype, np.float16, oracle.SUM, oracle.ROWWISE_ADAGRAD, lr=0.01)
+
+
+@pytest.mark.parametrize("gdtype", [np.float32, np.float16])
+@pytest.mark.parametrize("rows_hint", [True, False])
+def test_backward_many_tables_runs_across_spans_and_tiles(gdtype, rows_hint):
+    """Thirty tables of very different sizes (some without a lookup), two with a row that takes most of
+    the table's lookups: runs of tens of thousands of lookups crossing spans and tiles of the plan,
+    next to thousands of single-lookup runs. With and without the caller's bound on rows per table."""
+    rng = workloads.rng_for(445)
+    T, B = 30, 900
+    rows = [int(r) for r in rng.integers(1, 3000, size=T)]
+    Ds = [int(d) for d in rng.choice([4, 8, 16, 32, 64, 100, 128], size=T)]
+    W, wo, Do = helpers.float_tables(rng, rows, Ds, np.float16, -0.5, 0.5)
+    lengths = rng.integers(0, 60, size=T * B, dtype=np.int64)
+    for t in (3, 4, 17):                       # tables nobody looks up
+        lengths[t * B:(t + 1) * B] = 0
+    offsets = np.zeros(T * B + 1, dtype=np.int64)
+    np.cumsum(lengths, out=offsets[1:])
+    indices = np.zeros(int(offsets[-1]), dtype=np.int64)
+    for t in range(T):
+        a, b = int(offsets[t * B]), int(offsets[(t + 1) * B])
+        indices[a:b] = rng.integers(0, rows[t], size=b - a)
+        if t in (0, 11):
+            indices[a:b][rng.random(b - a) < 0.85] = rows[t] // 2
+    grad = rng.standard_normal((B, int(Do[-1]))).astype(np.float32)
+    if gdtype == np.float16:
+        grad = grad.astype(np.float16).astype(np.float32)
+    hs = np.zeros(T + 1, dtype=np.int64)
+    np.cumsum(np.asarray(rows, dtype=np.int64), out=hs[1:])
+    mom = (rng.random(int(hs[-1])) * 0.1).astype(np.float32)
+    _check(T, W, wo, Do, offsets, indices, None, grad, hs, mom, B, np.float16, gdtype, oracle.SUM,
+           oracle.ROWWISE_ADAGRAD, lr=0.01, rows_hint=rows_hint)
+
+
+def test_backward_run_of_only_bad_indices_leaves_row_zero_alone():
+    """Out-of-range ids are filed under row 0 of their table; when row 0 has no valid lookup it must
+    not be touched (with eps = 0 and zero state a zero gradient would otherwise divide by zero)."""
+    rng = workloads.rng_for(446)
+    rows, Ds, B = [50, 20], [64, 32], 12
+    T, W, wo, Do, offsets, indices, psw, grad, hs, mom = _backward_case(
+        rng, rows, Ds, B, 2, 6, np.float32, np.float32, oracle.SUM, oracle.ROWWISE_ADAGRAD, False)
+    mom[:] = 0
+    a, b = int(offsets[0]), int(offsets[B])
+    indices[a:b][indices[a:b] == 0] = 1          # nobody looks up row 0 of table 0 ...
+    bad = indices.copy()
+    bad[a:a + 3] = [50, 77, -1]                   # ... except three ids that are out of range
+    keep = np.ones(indices.size, dtype=np.float32)
+    keep[a:a + 3] = 0
+    W_ref, m_ref = W.copy(), mom.copy()
+    oracle.tbe_backward(W_ref, oracle.FP32, wo, Do, hs, B, np.where(keep > 0, indices, 1), offsets,
+                        grad, m_ref, hs[:-1], oracle.ROWWISE_ADAGRAD, 0.1, 0.0, keep)
+    dW, dm = _dev(W), _dev(mom)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    cabi.backward(dW, _dev(wo), _dev(Do), _dev(hs), 7, 64, _dev(bad), _dev(offsets), B, _dev(grad),
+                  oracle.ROWWISE_ADAGRAD, 0.1, 0.0, dm, _dev(hs[:-1].copy()), status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) & cabi.DEV_INDEX_OUT_OF_RANGE
+    got = dW.cpu().numpy()
+    assert np.array_equal(got[:64].view(np.uint32), W[:64].view(np.uint32))   # row 0 of table 0: untouched
+    assert np.isfinite(got).all() and float(dm[0].item()) == 0.0
+    np.testing.assert_allclose(got, W_ref, rtol=1e-4, atol=1e-6)
+    np.testing.assert_allclose(dm.cpu().numpy(), m_ref, rtol=1e-4, atol=1e-7)
 
 
 def test_backward_int32_indices_wide_rows():
@@ -167,7 +276,7 @@ def test_backward_named_training_config_scaled_down():
     grad = rng.standard_normal((B, T * D)).astype(np.float32)
     mom = np.zeros(T * E, dtype=np.float32)
     _check(T, W, wo, Do, inp.offsets, inp.indices, None, grad, hs, mom, B, np.float16, np.float32,
-           oracle.SUM, oracle.ROWWISE_ADAGRAD, lr=0.01)
+           oracle.SUM, oracle.ROWWISE_ADAGRAD, lr=0.01, update_rtol=1e-2)
 
 
 def test_backward_waits_for_the_gradient_event():

@@ -16,10 +16,10 @@ from torchlib_xpu_b200 import cabi, workloads
 pytestmark = pytest.mark.gpu
 
 
-def _sort_static(keys, vals, bits):
+def _sort_static(keys, vals, bits, outs=None):
     """Calls the entry point through the C ABI with raw pointers; the outputs are ordinary tensors
     the caller owns (the entry point itself allocates nothing)."""
-    keys_out, vals_out = torch.empty_like(keys), torch.empty_like(vals)
+    keys_out, vals_out = outs if outs is not None else (torch.empty_like(keys), torch.empty_like(vals))
     st = cabi.lib().b200tbe_radix_sort_pairs_static(
         keys.data_ptr(), vals.data_ptr(), keys_out.data_ptr(), vals_out.data_ptr(), keys.numel(),
         keys.element_size(), bits, torch.cuda.current_stream().cuda_stream)
@@ -38,11 +38,21 @@ def test_static_sort_matches_the_ordinary_entry_point_twice_in_a_row():
         k_dev = torch.from_numpy(keys.astype(dtype)).cuda()
         v_dev = torch.from_numpy(vals).cuda()
         want_k, want_v = cabi.radix_sort_pairs(k_dev.clone(), v_dev.clone(), bits)
-        st, got_k, got_v = _sort_static(k_dev.clone(), v_dev.clone(), bits)
+        k_in, v_in = k_dev.clone(), v_dev.clone()
+        outs = (torch.empty_like(k_in), torch.empty_like(v_in))
         torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]
+        st, got_k, got_v = _sort_static(k_in, v_in, bits, outs)
+        torch.cuda.synchronize()
+        # every buffer was in place before the call: the device's free memory must not have moved
+        assert torch.cuda.mem_get_info()[0] >= free_before
         assert st == 0
-        # integer work: bit-exact, as in the other sort tests
+        # integer work: bit-exact, as in the other sort tests: against the ordinary entry point ...
         assert torch.equal(got_k, want_k) and torch.equal(got_v, want_v)
+        # ... and against a stable CPU sort of the same pairs
+        order = np.argsort(keys.astype(np.uint64) & np.uint64((1 << bits) - 1), kind="stable")
+        assert np.array_equal(got_k.cpu().numpy(), keys.astype(dtype)[order])
+        assert np.array_equal(got_v.cpu().numpy(), vals[order])
 
 
 def test_static_sort_rejects_sizes_beyond_its_capacity():

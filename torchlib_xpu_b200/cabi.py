@@ -64,15 +64,7 @@ class BackwardParams(ctypes.Structure):
         ("index_bytes", ctypes.c_int32), ("pooling_mode", ctypes.c_int32),
         ("optimizer", ctypes.c_int32), ("learning_rate", ctypes.c_float), ("eps", ctypes.c_float),
         ("scratch", _c_void_p), ("scratch_bytes", ctypes.c_size_t), ("status", _c_void_p),
-        ("grad_ready_event", _c_void_p),
-    ]
-
-
-class ExchangePullParams(ctypes.Structure):
-    _fields_ = [
-        ("srcs", _c_void_p * MAX_DESTS), ("dst", _c_void_p), ("src_stride_bytes", ctypes.c_int64),
-        ("src_col_offset_bytes", ctypes.c_int64), ("dst_stride_bytes", ctypes.c_int64),
-        ("rows_per_src", ctypes.c_int64), ("row_bytes", ctypes.c_int64), ("num_srcs", ctypes.c_int32),
+        ("grad_ready_event", _c_void_p), ("max_table_rows", ctypes.c_int64),
     ]
 
 
@@ -97,8 +89,9 @@ class JaggedShape(ctypes.Structure):
 EXPORTS = (
     "b200tbe_status_string", "b200tbe_abi_version", "b200tbe_forward", "b200tbe_nbit_forward",
     "b200tbe_backward_scratch_bytes", "b200tbe_backward", "b200tbe_radix_sort_scratch_bytes",
-    "b200tbe_radix_sort_pairs", "b200tbe_radix_sort_pairs_static_max",
-    "b200tbe_radix_sort_pairs_static", "b200tbe_exchange_pull", "b200tbe_exchange_push", "b200tbe_permute_segments", "b200tbe_quantized_row_bytes",
+    "b200tbe_radix_sort_pairs", "b200tbe_radix_sort_segments_scratch_bytes",
+    "b200tbe_radix_sort_segments", "b200tbe_radix_sort_pairs_static_max",
+    "b200tbe_radix_sort_pairs_static", "b200tbe_exchange_push", "b200tbe_permute_segments", "b200tbe_quantized_row_bytes",
     "b200tbe_quantize_rows", "b200tbe_dequantize_rows", "b200tbe_nv12_to_rgb", "b200tbe_jagged_to_padded_dense", "b200tbe_dense_to_jagged",
     "b200tbe_jagged_dense_elementwise_add",
 )
@@ -124,18 +117,23 @@ def lib() -> ctypes.CDLL:
         _lib.b200tbe_status_string.restype = ctypes.c_char_p
         _lib.b200tbe_status_string.argtypes = [ctypes.c_int]
         _lib.b200tbe_backward_scratch_bytes.restype = ctypes.c_size_t
-        _lib.b200tbe_backward_scratch_bytes.argtypes = [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32]
+        _lib.b200tbe_backward_scratch_bytes.argtypes = [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32,
+                                                        ctypes.c_int32]
         _lib.b200tbe_radix_sort_scratch_bytes.restype = ctypes.c_size_t
         _lib.b200tbe_radix_sort_scratch_bytes.argtypes = [ctypes.c_int64]
         _lib.b200tbe_radix_sort_pairs.argtypes = [
             _c_void_p, _c_void_p, _c_void_p, _c_void_p, ctypes.c_int64, ctypes.c_int32,
             ctypes.c_int32, _c_void_p, ctypes.c_size_t, _c_void_p]
+        _lib.b200tbe_radix_sort_segments_scratch_bytes.restype = ctypes.c_size_t
+        _lib.b200tbe_radix_sort_segments_scratch_bytes.argtypes = [ctypes.c_int64, ctypes.c_int32]
+        _lib.b200tbe_radix_sort_segments.argtypes = [
+            _c_void_p, _c_void_p, _c_void_p, _c_void_p, ctypes.c_int64, _c_void_p, ctypes.c_int32,
+            ctypes.c_int32, ctypes.c_int32, _c_void_p, ctypes.c_size_t, _c_void_p]
         _lib.b200tbe_radix_sort_pairs_static_max.restype = ctypes.c_int64
         _lib.b200tbe_radix_sort_pairs_static_max.argtypes = []
         _lib.b200tbe_radix_sort_pairs_static.argtypes = [
             _c_void_p, _c_void_p, _c_void_p, _c_void_p, ctypes.c_int64, ctypes.c_int32,
             ctypes.c_int32, _c_void_p]
-        _lib.b200tbe_exchange_pull.argtypes = [ctypes.POINTER(ExchangePullParams), _c_void_p]
         _lib.b200tbe_exchange_push.argtypes = [ctypes.POINTER(ExchangePushParams), _c_void_p]
         _lib.b200tbe_permute_segments.argtypes = [_c_void_p] * 5 + [ctypes.c_int64, ctypes.c_int64] + \
             [ctypes.c_int32] * 3 + [_c_void_p]
@@ -243,18 +241,20 @@ def nbit_forward(dev_weights, weights_offsets, weights_tys, D_offsets, total_D, 
     return out
 
 
-def backward_scratch_bytes(num_indices: int, total_hash_size_bits: int, max_D: int) -> int:
-    return int(lib().b200tbe_backward_scratch_bytes(num_indices, total_hash_size_bits, max_D))
+def backward_scratch_bytes(num_indices: int, total_hash_size_bits: int, max_D: int, T: int) -> int:
+    return int(lib().b200tbe_backward_scratch_bytes(num_indices, total_hash_size_bits, max_D, T))
 
 
 def backward(dev_weights, weights_offsets, D_offsets, hash_size_cumsum, total_hash_size_bits, max_D,
              indices, offsets, B, grad_output, optimizer, learning_rate, eps=0.0, momentum1=None,
              momentum1_offsets=None, pooling_mode=POOL_SUM, per_sample_weights=None, scratch=None,
-             status=None, grad_col_offset=0, grad_ready_event=None):
-    """b200tbe_backward over torch tensors; dev_weights and momentum1 are updated in place."""
+             status=None, grad_col_offset=0, grad_ready_event=None, max_table_rows=0):
+    """b200tbe_backward over torch tensors; dev_weights and momentum1 are updated in place.
+    max_table_rows (rows of the largest table, 0 = unknown) lets the sort skip the key bits that
+    only tell tables apart."""
     T = weights_offsets.numel()
     n = indices.numel()
-    need = backward_scratch_bytes(n, total_hash_size_bits, max_D)
+    need = backward_scratch_bytes(n, total_hash_size_bits, max_D, T)
     if scratch is None:
         scratch = torch.empty(max(need, 256), dtype=torch.uint8, device=dev_weights.device)
     p = BackwardParams()
@@ -274,6 +274,7 @@ def backward(dev_weights, weights_offsets, D_offsets, hash_size_cumsum, total_ha
     p.status = _p(status)
     # a recorded torch.cuda.Event: the gradient matrix is complete once it has fired
     p.grad_ready_event = grad_ready_event.cuda_event if grad_ready_event is not None else None
+    p.max_table_rows = int(max_table_rows)
     check(lib().b200tbe_backward(ctypes.byref(p), _stream()), "b200tbe_backward")
     return scratch
 
@@ -291,17 +292,20 @@ def radix_sort_pairs(keys, vals, key_bits):
     return keys_out, vals_out
 
 
-def exchange_pull(src_ptrs, dst, src_stride_bytes, src_col_offset_bytes, rows_per_src, row_bytes):
-    """b200tbe_exchange_pull: src_ptrs are raw device addresses (peer-mapped buffers), dst a tensor
-    of [len(src_ptrs) * rows_per_src, row_bytes / element size]."""
-    p = ExchangePullParams()
-    for i, ptr in enumerate(src_ptrs):
-        p.srcs[i] = int(ptr)
-    p.dst = _p(dst)
-    p.src_stride_bytes, p.src_col_offset_bytes = src_stride_bytes, src_col_offset_bytes
-    p.dst_stride_bytes = dst.stride(0) * dst.element_size()
-    p.rows_per_src, p.row_bytes, p.num_srcs = rows_per_src, row_bytes, len(src_ptrs)
-    check(lib().b200tbe_exchange_pull(ctypes.byref(p), _stream()), "b200tbe_exchange_pull")
+def radix_sort_segments(keys, vals, seg_offsets, key_bits):
+    """Stable sort of every segment [seg_offsets[s], seg_offsets[s+1]) of (keys, vals) by the low
+    key_bits bits. keys and vals int32; seg_offsets int32/int64 on the device. Returns new
+    (keys, vals); the inputs are clobbered."""
+    n = keys.numel()
+    num_segments = seg_offsets.numel() - 1
+    keys_out, vals_out = torch.empty_like(keys), torch.empty_like(vals)
+    need = int(lib().b200tbe_radix_sort_segments_scratch_bytes(n, num_segments))
+    scratch = torch.empty(max(need, 256), dtype=torch.uint8, device=keys.device)
+    check(lib().b200tbe_radix_sort_segments(_p(keys), _p(vals), _p(keys_out), _p(vals_out), n,
+                                            _p(seg_offsets), seg_offsets.element_size(), num_segments,
+                                            key_bits, _p(scratch), scratch.numel(), _stream()),
+          "b200tbe_radix_sort_segments")
+    return keys_out, vals_out
 
 
 def exchange_push(src, dst_ptrs, dst_stride_bytes, dst_row_offset, block_bytes):

@@ -1,7 +1,7 @@
 // Version and status strings of the C ABI.
 #include "common.cuh"
 
-extern "C" int b200tbe_abi_version(void) { return 2; }
+extern "C" int b200tbe_abi_version(void) { return 3; }
 
 extern "C" const char* b200tbe_status_string(int status) {
   switch (status) {

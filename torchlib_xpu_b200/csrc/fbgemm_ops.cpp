@@ -20,6 +20,8 @@
 #include <torch/library.h>
 #include <torch/csrc/autograd/custom_function.h>
 
+#include <mutex>
+#include <unordered_map>
 #include <vector>
 
 #include "b200tbe.h"
@@ -68,6 +70,92 @@ int index_bytes_of(const Tensor& indices, const Tensor& offsets) {
 }
 
 bool is_empty_or_undefined(const Tensor& t) { return !t.defined() || t.numel() == 0; }
+
+// ---- facts about long-lived index tables, read from the device once ----------------------------
+// The lookup ops receive hash_size_cumsum, weights_placements and weights_offsets as DEVICE tensors
+// on every call. What the kernels need from them on the host side (row counts for range checks, the
+// largest table for the sort, "all placements are DEVICE") does not change while the tensor is not
+// written, so it is read back once -- one synchronising copy on the first call -- and remembered
+// under the tensor's storage address, size and version counter.
+struct TensorKey {
+  const void* ptr;
+  int64_t numel;
+  uint64_t version;
+  int device;
+  bool operator==(const TensorKey& o) const {
+    return ptr == o.ptr && numel == o.numel && version == o.version && device == o.device;
+  }
+};
+struct TensorKeyHash {
+  size_t operator()(const TensorKey& k) const {
+    return std::hash<const void*>()(k.ptr) ^ (std::hash<int64_t>()(k.numel) * 31) ^
+           (std::hash<uint64_t>()(k.version) * 131) ^ static_cast<size_t>(k.device);
+  }
+};
+TensorKey key_of(const Tensor& t) {
+  return {t.data_ptr(), t.numel(), static_cast<uint64_t>(t._version()), t.get_device()};
+}
+
+template <typename V>
+class FactCache {
+ public:
+  template <typename Make>
+  V get(const Tensor& t, Make make) {
+    const TensorKey k = key_of(t);
+    {
+      std::lock_guard<std::mutex> lock(mu_);
+      auto it = map_.find(k);
+      if (it != map_.end()) return it->second;
+    }
+    V v = make();
+    std::lock_guard<std::mutex> lock(mu_);
+    if (map_.size() >= 256) map_.clear();   // tables come and go; the facts are cheap to rebuild
+    map_.emplace(k, v);
+    return v;
+  }
+
+ private:
+  std::mutex mu_;
+  std::unordered_map<TensorKey, V, TensorKeyHash> map_;
+};
+
+struct TableRows {
+  Tensor rows_per_table;   // [T] int64 on the device
+  int64_t max_rows;
+};
+
+TableRows table_rows_of(const Tensor& hash_size_cumsum) {
+  static FactCache<TableRows> cache;
+  return cache.get(hash_size_cumsum, [&] {
+    const int64_t n = hash_size_cumsum.numel();
+    Tensor rows = (hash_size_cumsum.slice(0, 1, n) - hash_size_cumsum.slice(0, 0, n - 1)).contiguous();
+    const int64_t max_rows = n > 1 ? rows.max().item<int64_t>() : 0;
+    return TableRows{rows, max_rows};
+  });
+}
+
+// One int32 per device that the kernels OR B200TBE_DEV_* bits into (an index out of range, a row
+// shape a kernel cannot take). Nothing reads it on the hot path; fbgemm::b200tbe_pop_device_status
+// returns and clears it.
+Tensor device_status(const at::Device& device) {
+  static std::mutex mu;
+  static std::unordered_map<int, Tensor> words;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = words.find(device.index());
+  if (it != words.end()) return it->second;
+  Tensor w = at::zeros({1}, at::TensorOptions().dtype(at::kInt).device(device));
+  words.emplace(device.index(), w);
+  return w;
+}
+
+int64_t pop_device_status(const Tensor& like) {
+  TORCH_CHECK(like.is_cuda(), "b200tbe_pop_device_status takes any CUDA tensor of the device to query");
+  c10::cuda::CUDAGuard guard(like.device());
+  Tensor w = device_status(like.device());
+  const int64_t bits = w.item<int32_t>();   // synchronises with the current stream
+  if (bits != 0) w.zero_();
+  return bits;
+}
 
 // ---- jagged ---------------------------------------------------------------------------------
 
@@ -236,8 +324,10 @@ void check_placements(const Tensor& uvm_weights, const Tensor& lxu_cache_weights
               "uvm_weights must be empty: all tables live in dev_weights (HBM)");
   TORCH_CHECK(is_empty_or_undefined(lxu_cache_weights), "lxu_cache_weights must be empty: no cache");
   if (weights_placements.defined() && weights_placements.numel() > 0) {
-    TORCH_CHECK(weights_placements.to(at::kCPU).eq(0).all().item<bool>(),
-                "weights_placements must be all DEVICE (0)");
+    static FactCache<bool> cache;   // read back once per placements tensor, not once per call
+    const bool all_device = cache.get(
+        weights_placements, [&] { return weights_placements.to(at::kCPU).eq(0).all().item<bool>(); });
+    TORCH_CHECK(all_device, "weights_placements must be all DEVICE (0)");
   }
 }
 
@@ -269,6 +359,16 @@ Tensor tbe_forward(const TbeCommon& c) {
     TORCH_CHECK(c.indice_weights->scalar_type() == at::kFloat, "indice_weights must be float32");
     TORCH_CHECK(c.indice_weights->numel() == c.indices.numel(), "one weight per index");
     p.per_sample_weights = c.indice_weights->data_ptr<float>();
+  }
+  // ids are range-checked against the tables' row counts; a bad id is skipped and flagged
+  Tensor rows_keepalive, status_word;
+  if (c.hash_size_cumsum.defined() && c.hash_size_cumsum.numel() == T + 1 && T > 0) {
+    check_cuda_contig(c.hash_size_cumsum, "hash_size_cumsum");
+    TORCH_CHECK(c.hash_size_cumsum.scalar_type() == at::kLong, "hash_size_cumsum must be int64");
+    rows_keepalive = table_rows_of(c.hash_size_cumsum).rows_per_table;
+    status_word = device_status(c.dev_weights.device());
+    p.rows_per_table = rows_keepalive.data_ptr<int64_t>();
+    p.status = status_word.data_ptr<int32_t>();
   }
   p.outputs[0] = out.data_ptr();
   p.output_stride = c.total_D;
@@ -305,7 +405,8 @@ void tbe_backward(const TbeCommon& c, const Tensor& grad_in, const OptimizerArgs
   c10::cuda::CUDAGuard guard(c.dev_weights.device());
   const size_t need = b200tbe_backward_scratch_bytes(c.indices.numel(),
                                                      static_cast<int32_t>(c.total_hash_size_bits),
-                                                     static_cast<int32_t>(c.max_D));
+                                                     static_cast<int32_t>(c.max_D),
+                                                     static_cast<int32_t>(T));
   Tensor scratch = at::empty({static_cast<int64_t>(need)}, c.dev_weights.options().dtype(at::kByte));
   b200tbe_backward_params p{};
   p.dev_weights = c.dev_weights.data_ptr();
@@ -341,6 +442,9 @@ void tbe_backward(const TbeCommon& c, const Tensor& grad_in, const OptimizerArgs
   p.eps = static_cast<float>(o.eps);
   p.scratch = scratch.data_ptr();
   p.scratch_bytes = need;
+  p.max_table_rows = table_rows_of(c.hash_size_cumsum).max_rows;
+  Tensor status_word = device_status(c.dev_weights.device());
+  p.status = status_word.data_ptr<int32_t>();
   check_status(b200tbe_backward(&p, current_stream()), "split_embedding lookup backward");
 }
 
@@ -509,6 +613,39 @@ Tensor int_nbit_split_embedding_codegen_lookup_function(
   p.max_D = static_cast<int32_t>(std::max({max_int2_D, max_int4_D, max_int8_D, max_float16_D,
                                            max_float32_D}));
   p.row_alignment = static_cast<int32_t>(row_alignment.value_or(16));
+  // Row counts for the range check: the op's argument list does not carry them, but a table ends no
+  // later than where the nearest following table begins (or dev_weights ends), so
+  // rows_t <= bytes_t / stride_t: an id beyond that would read another table's bytes.
+  Tensor rows_keepalive, status_word;
+  if (T > 0) {
+    static FactCache<Tensor> cache;
+    const int64_t total_bytes = dev_weights.numel();
+    const int32_t align = p.row_alignment;
+    rows_keepalive = cache.get(weights_offsets, [&] {
+      const Tensor wo = weights_offsets.to(at::kCPU), ty = weights_tys.to(at::kCPU), Do = D_offsets.to(at::kCPU);
+      Tensor rows = at::empty({T}, at::TensorOptions().dtype(at::kLong));
+      for (int64_t t = 0; t < T; ++t) {
+        const int64_t begin = wo.data_ptr<int64_t>()[t];
+        int64_t end = total_bytes;   // tables need not be stored in table order
+        for (int64_t u = 0; u < T; ++u) {
+          const int64_t b = wo.data_ptr<int64_t>()[u];
+          if (b > begin && b < end) end = b;
+        }
+        const int32_t D = Do.data_ptr<int32_t>()[t + 1] - Do.data_ptr<int32_t>()[t];
+        const int code = ty.data_ptr<uint8_t>()[t];
+        int64_t stride = b200tbe_quantized_row_bytes(D, code, align);
+        if (stride <= 0) {   // float tables: no header
+          const int64_t raw = static_cast<int64_t>(D) * (code == B200TBE_FP16 ? 2 : 4);
+          stride = (raw + align - 1) / align * align;
+        }
+        rows.data_ptr<int64_t>()[t] = stride > 0 && end > begin ? (end - begin) / stride : 0;
+      }
+      return rows.to(dev_weights.device());
+    });
+    status_word = device_status(dev_weights.device());
+    p.rows_per_table = rows_keepalive.data_ptr<int64_t>();
+    p.status = status_word.data_ptr<int32_t>();
+  }
   p.output_dtype = static_cast<int32_t>(output_dtype);
   p.index_bytes = index_bytes_of(indices, offsets);
   p.pooling_mode = static_cast<int32_t>(pooling_mode);
@@ -613,6 +750,9 @@ TORCH_LIBRARY_FRAGMENT(fbgemm, m) {
       "Tensor? indice_weights, int output_dtype=1, Tensor? lxu_cache_weights=None, "
       "Tensor? lxu_cache_locations=None, int? row_alignment=None, int? max_float8_D=0, "
       "int? fp8_exponent_bits=-1, int? fp8_exponent_bias=-1) -> Tensor");
+  // Not an fbgemm_gpu operator: returns, and clears, the B200TBE_DEV_* bits the lookup kernels have
+  // raised on the device of `like` since the last call (0: none). Synchronises.
+  m.def("b200tbe_pop_device_status(Tensor like) -> int");
 }
 
 TORCH_LIBRARY_IMPL(fbgemm, CUDA, m) {
@@ -629,6 +769,7 @@ TORCH_LIBRARY_IMPL(fbgemm, CUDA, m) {
   m.impl("FusedNBitRowwiseQuantizedSBHalfToFloatOrHalf", TORCH_FN(fused_nbit_to_float_or_half));
   m.impl("int_nbit_split_embedding_codegen_lookup_function",
          TORCH_FN(int_nbit_split_embedding_codegen_lookup_function));
+  m.impl("b200tbe_pop_device_status", TORCH_FN(pop_device_status));
 }
 
 // The training lookups carry their own autograd node, so they sit on the Autograd key.

@@ -1,23 +1,32 @@
 // TBE backward with the optimizer fused: exact (one update per distinct row) SGD / row-wise Adagrad.
 //
-//   linearize   one warp per bag: key = hash_size_cumsum[t] + index, payload = bag id (or the
-//               lookup position when per-sample weights are in use)
-//   sort        radix_sort.cu over total_hash_size_bits bits; sorted order is (table, row), so
-//               while one table's rows are being reduced only that table's slice of the gradient
-//               matrix (B x D_t) is live and stays in L2
+// Rows of up to 512 elements (tbe_backward_sweep.cuh):
+//   plan        the lookups of table t are the index range [offsets[t*B], offsets[(t+1)*B]); every
+//               table's range is cut into tiles of 4096 lookups, described on the device
+//   linearize   key = row id, payload = bag id (or the lookup position when per-sample weights are
+//               in use); the table is implied by the position
+//   sort        radix_sort.cu, segmented: every table's range is sorted by row on its own, over the
+//               bits of the largest table only (22 bits for 4 M rows, whatever the number of tables)
+//   sweep       groups of lanes walk spans of 256 sorted lookups, summing gradient slices in
+//               registers and updating a row where its run of equal keys ends; since the sorted order
+//               is (table, row), only one table's B x D_t slice of the gradient matrix is live in L2
+//   finish      runs that cross span boundaries: their per-span partial sums are added in span order
+// Wider rows (up to 1024 elements):
+//   linearize   key = hash_size_cumsum[t] + index; flat sort over total_hash_size_bits bits
 //   segment     head flags + compaction give the start of every run of equal keys
-//   reduce      rows of up to 512 elements: tbe_backward_runs.cuh, a plain grid at high occupancy;
-//               a warp owns 32 consecutive runs, a group of lanes sums one run's gradient slices in
-//               registers and updates the row once, in place. Wider rows: persistent grid, one CTA
-//               per SM, on the shared-memory ring engine of tbe_stream.cuh (a warp takes 31
-//               consecutive runs and streams the gradient slices of their lookups through its ring).
-//               Runs longer than kLongRun are cut into chunks of kLongRun lookups: a second kernel
-//               streams each chunk through the ring into a partial row in scratch and a third adds a
-//               run's partials in chunk order and applies the update. Summation order is fixed by
-//               the data alone.
+//   reduce      persistent grid, one CTA per SM, on the shared-memory ring engine of tbe_stream.cuh
+//               (a warp takes 31 consecutive runs and streams the gradient slices of their lookups
+//               through its ring). Runs longer than kLongRun are cut into chunks of kLongRun lookups:
+//               a second kernel streams each chunk into a partial row in scratch and a third adds a
+//               run's partials in chunk order and applies the update.
+// Summation order is fixed by the data alone on both paths.
+#include <stdlib.h>
+
+#include <type_traits>
+
 #include "radix_sort.cuh"
 #include "scan.cuh"
-#include "tbe_stream.cuh"
+#include "tbe_bags.cuh"
 
 namespace b200tbe {
 namespace {
@@ -29,6 +38,19 @@ constexpr int kSegThreads = 1024;
 constexpr int kSegItems = 4;
 constexpr int kSegTile = kSegThreads * kSegItems;
 constexpr uint32_t kInvalidPayload = 0xffffffffu;
+
+inline int env_int(const char* name) {
+  const char* e = getenv(name);
+  return e ? atoi(e) : 0;
+}
+inline int sweep_tune_ctas() { return env_int("B200TBE_SWEEP_CTAS"); }
+inline int sweep_tune_l1() { return env_int("B200TBE_SWEEP_L1"); }
+
+// Widest digit of the segmented sort's passes.
+inline int sweep_digit_bits() {
+  const int v = env_int("B200TBE_SORT_DIGIT_BITS");
+  return v >= 4 && v <= 11 ? v : 11;
+}
 
 struct BwdDev {
   char* dev_weights;
@@ -61,8 +83,15 @@ struct BwdDev {
   uint32_t* long_run;        // [max_long] run id of each long run
   uint32_t* long_chunk0;     // [max_long] first chunk of each long run
   uint32_t* chunk_run;       // [max_chunks] slot (index into long_run) of each chunk
-  float* partials;           // [max_chunks][max_D]
+  float* partials;           // [max_chunks][max_D]; sweep path: [2 * spans][max_D] (head, tail slot)
   int32_t max_D;
+  // sweep path: the plan (tables -> tiles -> spans)
+  const uint32_t* seg_start;       // [T + 1] first sorted position of each table
+  const uint32_t* seg_tile_base;   // [T + 1] first tile of each table
+  const uint32_t* total_tiles;     // tiles in use
+  const uint4* tile_desc;          // [max_tiles] {begin, count, table, first tile of the table}
+  uint32_t* span_flags;            // [max_tiles * 16]
+  int32_t tune_prefetch_l1;        // experiment switch
 };
 
 // ---- linearize -----------------------------------------------------------------------------
@@ -370,7 +399,7 @@ __device__ __forceinline__ void apply_update_preloaded(const BwdDev& p, Acc4 (&a
   }
 }
 
-#include "tbe_backward_runs.cuh"
+#include "tbe_backward_sweep.cuh"
 
 struct RunGroup {
   int t;                 // table of every run in the group
@@ -378,7 +407,6 @@ struct RunGroup {
   int nvec;              // D / 4
   int copy_bytes;        // bytes of a gradient slice
   const char* grad_col;  // grad_output + column of table t, in bytes
-  int64_t hash0;         // hash_size_cumsum[t]
   int64_t bag0;          // t * B
 };
 
@@ -639,7 +667,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1)
       g.nvec = g.D >> 2;
       g.copy_bytes = g.D * static_cast<int>(sizeof(GT));
       g.grad_col = p.grad_output + (p.grad_col_offset + D_begin) * static_cast<int64_t>(sizeof(GT));
-      g.hash0 = 0;
       g.bag0 = static_cast<int64_t>(g.t) * p.B;
       const bool ok = (g.copy_bytes & 15) == 0 && (reinterpret_cast<uintptr_t>(g.grad_col) & 15) == 0 &&
                       g.nvec <= 32 * kVPL && g.copy_bytes <= kStageBytes && g.D > 0;
@@ -692,7 +719,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1)
     g.nvec = g.D >> 2;
     g.copy_bytes = g.D * static_cast<int>(sizeof(GT));
     g.grad_col = p.grad_output + (p.grad_col_offset + D_begin) * static_cast<int64_t>(sizeof(GT));
-    g.hash0 = 0;
     g.bag0 = static_cast<int64_t>(g.t) * p.B;
     const bool ok = (g.copy_bytes & 15) == 0 && (reinterpret_cast<uintptr_t>(g.grad_col) & 15) == 0 &&
                     g.nvec <= 32 * kVPL && g.copy_bytes <= kStageBytes && g.D > 0;
@@ -747,19 +773,24 @@ __global__ void __launch_bounds__(kBwdThreads) finish_long_runs_kernel(BwdDev p)
 
 size_t align256(size_t x) { return (x + 255) & ~size_t{255}; }
 
+// Rows of up to kSweepMaxD elements take the sweep path, wider ones the ring engine.
+constexpr int kSweepMaxD = 512;
+constexpr int kRingMaxD = 1024;
+
 struct ScratchLayout {
   size_t keys_a, keys_b, vals_a, vals_b, bag_of_pos, run_start, tile_heads, counters, long_run,
-      long_chunk0, chunk_run, partials, sort, total;
+      long_chunk0, chunk_run, partials, sort, plan, span_flags, total;
   int key_bytes;
-  int64_t max_long, max_chunks;
+  bool sweep;
+  int64_t max_long, max_chunks, max_tiles;
 };
 
-ScratchLayout layout_for(int64_t n, int bits, int max_D) {
-  ScratchLayout L;
-  L.key_bytes = bits <= 32 ? 4 : 8;
+ScratchLayout layout_for(int64_t n, int bits, int max_D, int T) {
+  ScratchLayout L{};
+  L.sweep = max_D <= kSweepMaxD;
+  L.key_bytes = (L.sweep || bits <= 32) ? 4 : 8;
   const size_t nn = static_cast<size_t>(n > 0 ? n : 1);
-  L.max_long = n / kLongRun + 1;
-  L.max_chunks = 2 * (n / kLongRun) + 2;
+  const size_t row = static_cast<size_t>(max_D > 0 ? max_D : 1) * 4;
   size_t at = 0;
   auto take = [&](size_t bytes) {
     const size_t here = at;
@@ -771,14 +802,25 @@ ScratchLayout layout_for(int64_t n, int bits, int max_D) {
   L.vals_a = take(nn * 4);
   L.vals_b = take(nn * 4);
   L.bag_of_pos = take(nn * 4);
-  L.run_start = take((nn + 1) * 4);
-  L.tile_heads = take(static_cast<size_t>((n + kSegTile - 1) / kSegTile + 1) * 4);
   L.counters = take(256);
-  L.long_run = take(static_cast<size_t>(L.max_long) * 4);
-  L.long_chunk0 = take(static_cast<size_t>(L.max_long) * 4);
-  L.chunk_run = take(static_cast<size_t>(L.max_chunks) * 4);
-  L.partials = take(static_cast<size_t>(L.max_chunks) * static_cast<size_t>(max_D > 0 ? max_D : 1) * 4);
-  L.sort = take(radix_sort_scratch_bytes(n));
+  if (L.sweep) {
+    // every table's last tile may be partial
+    L.max_tiles = sort_plan_max_tiles(n, T);
+    L.plan = take(sort_plan_bytes(n, T));
+    L.span_flags = take(static_cast<size_t>(L.max_tiles) * kSpansPerTile * 4);
+    L.partials = take(static_cast<size_t>(L.max_tiles) * kSpansPerTile * 2 * row);
+    L.sort = take(radix_sort_planned_scratch_bytes(L.max_tiles));
+  } else {
+    L.max_long = n / kLongRun + 1;
+    L.max_chunks = 2 * (n / kLongRun) + 2;
+    L.run_start = take((nn + 1) * 4);
+    L.tile_heads = take(static_cast<size_t>((n + kSegTile - 1) / kSegTile + 1) * 4);
+    L.long_run = take(static_cast<size_t>(L.max_long) * 4);
+    L.long_chunk0 = take(static_cast<size_t>(L.max_long) * 4);
+    L.chunk_run = take(static_cast<size_t>(L.max_chunks) * 4);
+    L.partials = take(static_cast<size_t>(L.max_chunks) * row);
+    L.sort = take(radix_sort_scratch_bytes(n));
+  }
   L.total = at;
   return L;
 }
@@ -788,50 +830,27 @@ int persistent_grid() {
   return kNumSMs * 6;
 }
 
+// ---- wide rows: ring engine ---------------------------------------------------------------------
 template <typename KeyT, typename WT, typename GT, int kVPL>
 int run_reduce(const BwdDev& d, cudaStream_t stream) {
   const int grid = persistent_grid();
-  if (d.max_D <= 512) {
-    // one warp per 32 runs; the run count is known on the device only, num_indices bounds it
-    const int64_t ctas = (d.num_indices + 32 * kRunWarps - 1) / (32 * kRunWarps);
-    if (ctas > 0x7fffffff) return B200TBE_ERR_TOO_LARGE;
-    const unsigned run_grid = static_cast<unsigned>(ctas > 0 ? ctas : 1);
-    const int chunk_grid = kNumSMs * run_ctas_per_sm<GT>();
-    if (d.per_sample_weights != nullptr || d.pooling_mode == B200TBE_POOL_MEAN) {
-      reduce_runs_groups_kernel<KeyT, WT, GT, true, 4><<<run_grid, kRunThreads, 0, stream>>>(d);
-      reduce_chunks_groups_kernel<KeyT, GT, true, 4><<<chunk_grid, kRunThreads, 0, stream>>>(d);
-    } else {
-      reduce_runs_groups_kernel<KeyT, WT, GT, false, 4><<<run_grid, kRunThreads, 0, stream>>>(d);
-      reduce_chunks_groups_kernel<KeyT, GT, false, 4><<<chunk_grid, kRunThreads, 0, stream>>>(d);
-    }
-  } else {
-    auto stream_kernel = reduce_runs_stream_kernel<KeyT, WT, GT, kVPL>;
-    if (cudaFuncSetAttribute(stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(kStreamSmemBytes)) != cudaSuccess)
-      return B200TBE_ERR_LAUNCH;
-    stream_kernel<<<kNumSMs, kStreamThreads, kStreamSmemBytes, stream>>>(d);
-    auto chunk_kernel = reduce_chunks_stream_kernel<KeyT, WT, GT, kVPL>;
-    if (cudaFuncSetAttribute(chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             static_cast<int>(kStreamSmemBytes)) != cudaSuccess)
-      return B200TBE_ERR_LAUNCH;
-    chunk_kernel<<<kNumSMs, kStreamThreads, kStreamSmemBytes, stream>>>(d);
-  }
+  auto stream_kernel = reduce_runs_stream_kernel<KeyT, WT, GT, kVPL>;
+  if (cudaFuncSetAttribute(stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(kStreamSmemBytes)) != cudaSuccess)
+    return B200TBE_ERR_LAUNCH;
+  stream_kernel<<<kNumSMs, kStreamThreads, kStreamSmemBytes, stream>>>(d);
+  auto chunk_kernel = reduce_chunks_stream_kernel<KeyT, WT, GT, kVPL>;
+  if (cudaFuncSetAttribute(chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(kStreamSmemBytes)) != cudaSuccess)
+    return B200TBE_ERR_LAUNCH;
+  chunk_kernel<<<kNumSMs, kStreamThreads, kStreamSmemBytes, stream>>>(d);
   finish_long_runs_kernel<KeyT, WT, GT, kVPL><<<grid, kBwdThreads, 0, stream>>>(d);
   return launch_status();
 }
 
-template <typename KeyT, typename WT, typename GT>
-int dispatch_vpl(const BwdDev& d, int slice_vecs_max, cudaStream_t stream) {
-  if (slice_vecs_max <= 32) return run_reduce<KeyT, WT, GT, 1>(d, stream);
-  if (slice_vecs_max <= 64) return run_reduce<KeyT, WT, GT, 2>(d, stream);
-  if (slice_vecs_max <= 128) return run_reduce<KeyT, WT, GT, 4>(d, stream);
-  if (slice_vecs_max <= 256) return run_reduce<KeyT, WT, GT, 8>(d, stream);
-  return B200TBE_ERR_UNSUPPORTED;
-}
-
 template <typename KeyT, typename IndexT>
-int run_backward(BwdDev d, const b200tbe_backward_params* p, const ScratchLayout& L, char* scratch,
-                 cudaStream_t stream) {
+int run_backward_wide(BwdDev d, const b200tbe_backward_params* p, const ScratchLayout& L, char* scratch,
+                      cudaStream_t stream) {
   const int64_t n = p->num_indices;
   KeyT* keys_a = reinterpret_cast<KeyT*>(scratch + L.keys_a);
   KeyT* keys_b = reinterpret_cast<KeyT*>(scratch + L.keys_b);
@@ -870,13 +889,115 @@ int run_backward(BwdDev d, const b200tbe_backward_params* p, const ScratchLayout
   if (p->grad_ready_event != nullptr &&
       cudaStreamWaitEvent(stream, static_cast<cudaEvent_t>(p->grad_ready_event), 0) != cudaSuccess)
     return B200TBE_ERR_LAUNCH;
-  const int grad_bytes = p->grad_dtype == B200TBE_FP32 ? 4 : 2;
-  const int slice_vecs_max = (p->max_D * grad_bytes + 15) / 16;
+  // a lane of the ring engine holds kVPL vectors of 4 ELEMENTS, whatever the gradient type:
+  // 1024 elements need 8
   const bool w32 = p->weights_dtype == B200TBE_FP32, g32 = p->grad_dtype == B200TBE_FP32;
-  if (w32 && g32) return dispatch_vpl<KeyT, float, float>(d, slice_vecs_max, stream);
-  if (!w32 && g32) return dispatch_vpl<KeyT, __half, float>(d, slice_vecs_max, stream);
-  if (w32 && !g32) return dispatch_vpl<KeyT, float, __half>(d, slice_vecs_max, stream);
-  return dispatch_vpl<KeyT, __half, __half>(d, slice_vecs_max, stream);
+  if (w32 && g32) return run_reduce<KeyT, float, float, 8>(d, stream);
+  if (!w32 && g32) return run_reduce<KeyT, __half, float, 8>(d, stream);
+  if (w32 && !g32) return run_reduce<KeyT, float, __half, 8>(d, stream);
+  return run_reduce<KeyT, __half, __half, 8>(d, stream);
+}
+
+// ---- rows of up to 512 elements: plan, segmented sort, sweep --------------------------------------
+template <typename WT, typename GT, bool kScaled, int GS, int kC>
+int launch_sweep(const BwdDev& d, int max_tiles, cudaStream_t stream) {
+  constexpr int kSpansPerCta = kSweepWarps * (32 / GS);
+  const int64_t ctas = static_cast<int64_t>(max_tiles) * (kSpansPerTile / kSpansPerCta);
+  const int64_t spans = static_cast<int64_t>(max_tiles) * kSpansPerTile;
+  if (ctas > 0x7fffffff || spans / kSweepWarps > 0x7fffffff) return B200TBE_ERR_TOO_LARGE;
+  const int tune = sweep_tune_ctas();
+  if (std::is_same<WT, __half>::value && std::is_same<GT, __half>::value && !kScaled && GS == 16 && tune != 0) {
+    if (tune == 6)
+      sweep_runs_kernel<__half, __half, false, 16, 2, 6><<<static_cast<unsigned>(ctas), kSweepThreads, 0, stream>>>(d);
+    else if (tune == 10)
+      sweep_runs_kernel<__half, __half, false, 16, 2, 10><<<static_cast<unsigned>(ctas), kSweepThreads, 0, stream>>>(d);
+    else
+      sweep_runs_kernel<__half, __half, false, 16, 2, 5><<<static_cast<unsigned>(ctas), kSweepThreads, 0, stream>>>(d);
+  } else {
+    sweep_runs_kernel<WT, GT, kScaled, GS, kC, sweep_ctas_per_sm<GT, kC>()>
+        <<<static_cast<unsigned>(ctas), kSweepThreads, 0, stream>>>(d);
+  }
+  finish_open_runs_kernel<WT, GS, kC>
+      <<<static_cast<unsigned>(spans / kSweepWarps), kSweepThreads, 0, stream>>>(d);
+  return launch_status();
+}
+
+template <typename WT, typename GT, bool kScaled>
+int dispatch_sweep_shape(const BwdDev& d, int max_tiles, cudaStream_t stream) {
+  // lanes per row x quads per lane: the smallest group that holds max_D elements
+  if (d.max_D <= 64) return launch_sweep<WT, GT, kScaled, 8, 2>(d, max_tiles, stream);
+  if (d.max_D <= 128) return launch_sweep<WT, GT, kScaled, 16, 2>(d, max_tiles, stream);
+  if (d.max_D <= 256) return launch_sweep<WT, GT, kScaled, 32, 2>(d, max_tiles, stream);
+  return launch_sweep<WT, GT, kScaled, 32, 4>(d, max_tiles, stream);
+}
+
+template <typename WT, typename GT>
+int dispatch_sweep_scaled(const BwdDev& d, int max_tiles, cudaStream_t stream) {
+  if (d.per_sample_weights != nullptr || d.pooling_mode == B200TBE_POOL_MEAN)
+    return dispatch_sweep_shape<WT, GT, true>(d, max_tiles, stream);
+  return dispatch_sweep_shape<WT, GT, false>(d, max_tiles, stream);
+}
+
+int ceil_log2(int64_t x) {
+  int b = 0;
+  while (b < 62 && (int64_t{1} << b) < x) ++b;
+  return b;
+}
+
+template <typename IndexT>
+int run_backward_sweep(BwdDev d, const b200tbe_backward_params* p, const ScratchLayout& L, char* scratch,
+                       cudaStream_t stream) {
+  const int64_t n = p->num_indices;
+  uint32_t* keys_a = reinterpret_cast<uint32_t*>(scratch + L.keys_a);
+  uint32_t* keys_b = reinterpret_cast<uint32_t*>(scratch + L.keys_b);
+  uint32_t* vals_a = reinterpret_cast<uint32_t*>(scratch + L.vals_a);
+  uint32_t* vals_b = reinterpret_cast<uint32_t*>(scratch + L.vals_b);
+  const int max_tiles = static_cast<int>(L.max_tiles);
+  const bool weighted = p->per_sample_weights != nullptr;
+
+  // bits that differ inside a table: those of the largest table's last row id
+  int key_bits = p->total_hash_size_bits < 32 ? p->total_hash_size_bits : 32;
+  if (p->max_table_rows > 0 && ceil_log2(p->max_table_rows) < key_bits) key_bits = ceil_log2(p->max_table_rows);
+  if (key_bits < 1) key_bits = 1;
+
+  // the lookups of table t are positions [offsets[t * B], offsets[(t + 1) * B])
+  SortPlan plan{};
+  const uint32_t* seg_start = nullptr;
+  int st = build_sort_plan(p->offsets, p->index_bytes, p->T, p->B, n, scratch + L.plan, p->status, &plan,
+                           &seg_start, stream);
+  if (st != B200TBE_OK) return st;
+  const int64_t bags = static_cast<int64_t>(p->T) * p->B;
+  const int64_t lin_ctas = (bags + 32 * kBwdWarps - 1) / (32 * kBwdWarps);
+  if (lin_ctas > 0x7fffffff) return B200TBE_ERR_TOO_LARGE;
+  if (weighted) {
+    linearize_rows_kernel<IndexT, true>
+        <<<static_cast<unsigned>(lin_ctas), kBwdThreads, 0, stream>>>(d, key_bits, keys_a, vals_a);
+  } else {
+    linearize_rows_kernel<IndexT, false>
+        <<<static_cast<unsigned>(lin_ctas), kBwdThreads, 0, stream>>>(d, key_bits, keys_a, vals_a);
+  }
+  bool in_b = false;
+  st = radix_sort_pairs_planned(keys_a, vals_a, keys_b, vals_b, n, key_bits, sweep_digit_bits(),
+                                          plan, scratch + L.sort, radix_sort_planned_scratch_bytes(max_tiles),
+                                          &in_b, stream);
+  if (st != B200TBE_OK) return st;
+  d.sorted_keys = in_b ? keys_b : keys_a;
+  d.sorted_vals = in_b ? vals_b : vals_a;
+  d.seg_start = seg_start;
+  d.seg_tile_base = plan.seg_tile_base;
+  d.total_tiles = plan.total_tiles;
+  d.tile_desc = plan.tile_desc;
+  d.span_flags = reinterpret_cast<uint32_t*>(scratch + L.span_flags);
+
+  // everything above needed only the indices; the gradients are read from here on
+  if (p->grad_ready_event != nullptr &&
+      cudaStreamWaitEvent(stream, static_cast<cudaEvent_t>(p->grad_ready_event), 0) != cudaSuccess)
+    return B200TBE_ERR_LAUNCH;
+  const bool w32 = p->weights_dtype == B200TBE_FP32, g32 = p->grad_dtype == B200TBE_FP32;
+  if (w32 && g32) return dispatch_sweep_scaled<float, float>(d, max_tiles, stream);
+  if (!w32 && g32) return dispatch_sweep_scaled<__half, float>(d, max_tiles, stream);
+  if (w32 && !g32) return dispatch_sweep_scaled<float, __half>(d, max_tiles, stream);
+  return dispatch_sweep_scaled<__half, __half>(d, max_tiles, stream);
 }
 
 }  // namespace
@@ -885,14 +1006,15 @@ int run_backward(BwdDev d, const b200tbe_backward_params* p, const ScratchLayout
 using namespace b200tbe;
 
 extern "C" size_t b200tbe_backward_scratch_bytes(int64_t num_indices, int32_t total_hash_size_bits,
-                                                 int32_t max_D) {
-  if (num_indices < 0) return 0;
-  return layout_for(num_indices, total_hash_size_bits, max_D).total;
+                                                 int32_t max_D, int32_t T) {
+  if (num_indices < 0 || T < 0) return 0;
+  return layout_for(num_indices, total_hash_size_bits, max_D, T).total;
 }
 
 extern "C" int b200tbe_backward(const b200tbe_backward_params* p, b200tbe_stream_t stream_) {
   if (p == nullptr) return B200TBE_ERR_BAD_ARG;
-  if (p->T < 0 || p->B < 0 || p->max_D < 0 || p->num_indices < 0) return B200TBE_ERR_BAD_ARG;
+  if (p->T < 0 || p->B < 0 || p->max_D < 0 || p->num_indices < 0 || p->max_table_rows < 0)
+    return B200TBE_ERR_BAD_ARG;
   if (p->T == 0 || p->B == 0 || p->num_indices == 0) return B200TBE_OK;
   if (p->dev_weights == nullptr || p->weights_offsets == nullptr || p->D_offsets == nullptr ||
       p->hash_size_cumsum == nullptr || p->indices == nullptr || p->offsets == nullptr ||
@@ -912,19 +1034,22 @@ extern "C" int b200tbe_backward(const b200tbe_backward_params* p, b200tbe_stream
   if (p->total_hash_size_bits < 1 || p->total_hash_size_bits > 40) return B200TBE_ERR_UNSUPPORTED;
   if (p->num_indices >= (int64_t{1} << 31)) return B200TBE_ERR_TOO_LARGE;
   if (static_cast<int64_t>(p->T) * p->B >= (int64_t{1} << 32) - 1) return B200TBE_ERR_TOO_LARGE;
-  if (p->max_D % 4 != 0) return B200TBE_ERR_UNSUPPORTED;
+  if (p->max_D % 4 != 0 || p->max_D > kRingMaxD) return B200TBE_ERR_UNSUPPORTED;
   const int grad_bytes = p->grad_dtype == B200TBE_FP32 ? 4 : 2;
   // gradient slices are read as whole 16-byte vectors
-  if ((p->max_D * grad_bytes) % 16 != 0 || (p->grad_stride * grad_bytes) % 16 != 0 ||
-      (p->grad_col_offset * grad_bytes) % 16 != 0 || !aligned_to(p->grad_output, 16) ||
-      !aligned_to(p->dev_weights, 16))
+  if ((p->grad_stride * grad_bytes) % 16 != 0 || (p->grad_col_offset * grad_bytes) % 16 != 0 ||
+      !aligned_to(p->grad_output, 16) || !aligned_to(p->dev_weights, 16))
     return B200TBE_ERR_UNSUPPORTED;
-  const ScratchLayout L = layout_for(p->num_indices, p->total_hash_size_bits, p->max_D);
+  if (p->max_D > kSweepMaxD && (p->max_D * grad_bytes) % 16 != 0) return B200TBE_ERR_UNSUPPORTED;
+  // offsets of gradient slices inside one table's columns travel as 32-bit counts of 16 bytes
+  if (static_cast<int64_t>(p->B) * p->grad_stride * grad_bytes / 16 >= (int64_t{1} << 32) - 1)
+    return B200TBE_ERR_TOO_LARGE;
+  const ScratchLayout L = layout_for(p->num_indices, p->total_hash_size_bits, p->max_D, p->T);
   if (p->scratch == nullptr || p->scratch_bytes < L.total || !aligned_to(p->scratch, 256))
     return B200TBE_ERR_SCRATCH;
   char* scratch = static_cast<char*>(p->scratch);
 
-  BwdDev d;
+  BwdDev d{};
   d.dev_weights = static_cast<char*>(p->dev_weights);
   d.weights_offsets = p->weights_offsets;
   d.D_offsets = p->D_offsets;
@@ -946,22 +1071,24 @@ extern "C" int b200tbe_backward(const b200tbe_backward_params* p, b200tbe_stream
   d.learning_rate = p->learning_rate;
   d.eps = p->eps;
   d.status = p->status;
-  d.sorted_keys = nullptr;
-  d.sorted_vals = nullptr;
   d.bag_of_pos = reinterpret_cast<uint32_t*>(scratch + L.bag_of_pos);
-  d.run_start = reinterpret_cast<uint32_t*>(scratch + L.run_start);
   d.counters = reinterpret_cast<uint32_t*>(scratch + L.counters);
+  d.partials = reinterpret_cast<float*>(scratch + L.partials);
+  d.max_D = p->max_D;
+  d.tune_prefetch_l1 = sweep_tune_l1();
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  const bool i64 = p->index_bytes == 8;
+  if (L.sweep)
+    return i64 ? run_backward_sweep<int64_t>(d, p, L, scratch, stream)
+               : run_backward_sweep<int32_t>(d, p, L, scratch, stream);
+  d.run_start = reinterpret_cast<uint32_t*>(scratch + L.run_start);
   d.long_run = reinterpret_cast<uint32_t*>(scratch + L.long_run);
   d.long_chunk0 = reinterpret_cast<uint32_t*>(scratch + L.long_chunk0);
   d.chunk_run = reinterpret_cast<uint32_t*>(scratch + L.chunk_run);
-  d.partials = reinterpret_cast<float*>(scratch + L.partials);
-  d.max_D = p->max_D;
-  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  const bool k32 = L.key_bytes == 4, i64 = p->index_bytes == 8;
-  if (k32) {
-    return i64 ? run_backward<uint32_t, int64_t>(d, p, L, scratch, stream)
-               : run_backward<uint32_t, int32_t>(d, p, L, scratch, stream);
+  if (L.key_bytes == 4) {
+    return i64 ? run_backward_wide<uint32_t, int64_t>(d, p, L, scratch, stream)
+               : run_backward_wide<uint32_t, int32_t>(d, p, L, scratch, stream);
   }
-  return i64 ? run_backward<unsigned long long, int64_t>(d, p, L, scratch, stream)
-             : run_backward<unsigned long long, int32_t>(d, p, L, scratch, stream);
+  return i64 ? run_backward_wide<unsigned long long, int64_t>(d, p, L, scratch, stream)
+             : run_backward_wide<unsigned long long, int32_t>(d, p, L, scratch, stream);
 }

@@ -9,12 +9,12 @@ up with the pooled rows of its own slice of the batch (B / G bags) for ALL table
 separate collective on the forward path: b200tbe_forward writes each pooled vector straight into the
 destination rank's receive buffer through its peer mapping (plain 16-byte stores over NVLink), and a
 stream-ordered barrier closes the step. On the way back each rank stores the column blocks of its
-gradient rows into the owning ranks' matrices with b200tbe_exchange_push (b200tbe_exchange_pull
-moves the same bytes the other way round, slower), then runs the local fused backward.
+gradient rows into the owning ranks' matrices with b200tbe_exchange_push, then runs the local fused
+backward.
 
 `layout_*` below are pure index arithmetic and are what the CPU (gloo) tests exercise;
-`reference_exchange` is the same data movement as an all_to_all_single, used as the baseline on
-GPUs (NCCL) and as the checker on CPU (gloo).
+`reference_exchange` / `reference_gradient_exchange` are the same data movements as plain
+all_to_all_single calls (NCCL on GPUs, gloo on CPU): what the fused paths are compared with.
 """
 from __future__ import annotations
 
@@ -79,11 +79,9 @@ class PooledExchange:
         dev = torch.device("cuda", torch.cuda.current_device())
         # what this rank receives in the forward, and the gradient it hands back in the backward
         self.recv = symm_mem.empty((self.per, world * local_D), dtype=dtype, device=dev)
-        self.grad_slice = symm_mem.empty((self.per, world * local_D), dtype=dtype, device=dev)
+        self.grad_slice = torch.empty((self.per, world * local_D), dtype=dtype, device=dev)
         self._recv_hdl = symm_mem.rendezvous(self.recv, dist.group.WORLD)
-        self._grad_hdl = symm_mem.rendezvous(self.grad_slice, dist.group.WORLD)
         self.recv_ptrs = [int(p) for p in self._recv_hdl.buffer_ptrs]
-        self.grad_ptrs = [int(p) for p in self._grad_hdl.buffer_ptrs]
         # this rank's column block of every rank's gradients; the peers store into it
         self.grad_local = symm_mem.empty((B, local_D), dtype=dtype, device=dev)
         self._gradl_hdl = symm_mem.rendezvous(self.grad_local, dist.group.WORLD)
@@ -110,21 +108,20 @@ class PooledExchange:
                      output_dtype=self.dtype)
         self.barrier()
 
-    def gather_gradients(self, step, push: bool = True):
-        """Brings this rank's column block of every rank's gradient matrix into [B, local_D]. Every
-        rank stores the blocks of its own gradient rows into the owners' matrices (push: NVLink
-        stores stream, measured twice as fast as pulling the same bytes); push=False pulls instead.
-        The call must follow a barrier that follows the previous reader of grad_local on every rank
-        (the forward's barrier does), and ends with one."""
+    def push_gradients(self):
+        """Stores every owner's column block of this rank's gradient rows into that owner's matrix
+        (b200tbe_exchange_push: NVLink stores stream). No barrier: the caller orders it."""
         from . import cabi
 
         esz = self.grad_slice.element_size()
-        if push:
-            cabi.exchange_push(self.grad_slice, self.gradl_ptrs, self.local_D * esz, self.rank * self.per,
-                               self.local_D * esz)
-        else:
-            cabi.exchange_pull(self.grad_ptrs, self.grad_local, self.world * self.local_D * esz,
-                               self.rank * self.local_D * esz, self.per, self.local_D * esz)
+        cabi.exchange_push(self.grad_slice, self.gradl_ptrs, self.local_D * esz, self.rank * self.per,
+                           self.local_D * esz)
+
+    def gather_gradients(self, step=None):
+        """Brings this rank's column block of every rank's gradient matrix into [B, local_D]. The call
+        must follow a barrier that follows the previous reader of grad_local on every rank (the
+        forward's barrier does), and ends with one."""
+        self.push_gradients()
         self.barrier()
         return self.grad_local
 
@@ -163,17 +160,6 @@ def _exclusive_offsets(lengths_flat: torch.Tensor) -> torch.Tensor:
     off = torch.zeros(lengths_flat.numel() + 1, dtype=torch.int64, device=lengths_flat.device)
     torch.cumsum(lengths_flat, 0, out=off[1:])
     return off
-
-
-def reference_permute_segments(values, lengths_flat, perm):
-    """out segment j = in segment perm[j], in plain torch (any device): the checker of
-    b200tbe_permute_segments and the data movement of the CPU (gloo) tests."""
-    in_off = _exclusive_offsets(lengths_flat)
-    out_len = lengths_flat[perm]
-    out_off = _exclusive_offsets(out_len)
-    shift = in_off[:-1][perm] - out_off[:-1]
-    src = torch.arange(values.numel(), device=values.device) + torch.repeat_interleave(shift, out_len)
-    return values[src]
 
 
 def kernel_permute_segments(values, lengths_flat, perm):
@@ -225,7 +211,7 @@ def _distribute(lengths_dp, indices_dp, weights_dp, group, permute):
     return lengths_tw, offsets_tw, indices_tw, weights_tw
 
 
-def distribute_inputs(lengths_dp, indices_dp, weights_dp=None, group=None):
+def distribute_inputs(lengths_dp, indices_dp, weights_dp=None, group=None, permute=None):
     """From the data-parallel layout to the table-wise one (CUDA tensors, NCCL).
 
     lengths_dp [T_global, B / G]: bag lengths of this rank's slice of the global batch for every
@@ -234,10 +220,6 @@ def distribute_inputs(lengths_dp, indices_dp, weights_dp=None, group=None):
     [T_local * B + 1], ids and weights in bag order: the arguments of b200tbe_forward /
     b200tbe_backward. Two all_to_all_single calls (lengths, then ids with the sizes the lengths
     announce; one host read of the split sizes in between) and two segment permutations by
-    b200tbe_permute_segments."""
-    return _distribute(lengths_dp, indices_dp, weights_dp, group, kernel_permute_segments)
-
-
-def reference_distribute_inputs(lengths_dp, indices_dp, weights_dp=None, group=None):
-    """The same in plain torch on any backend (gloo on CPU): the checker."""
-    return _distribute(lengths_dp, indices_dp, weights_dp, group, reference_permute_segments)
+    b200tbe_permute_segments. `permute(values, lengths, perm)` replaces the kernel in tests that run
+    the collective logic on CPU ranks with a checker's permutation."""
+    return _distribute(lengths_dp, indices_dp, weights_dp, group, permute or kernel_permute_segments)

@@ -47,7 +47,11 @@ class SplitTableBatchedEmbeddingBagsCodegen(torch.nn.Module):
                  optimizer: OptimType = OptimType.EXACT_ROWWISE_ADAGRAD, learning_rate: float = 0.01,
                  eps: float = 1e-8, pooling_mode: PoolingMode = PoolingMode.SUM,
                  weights_precision: SparseType = SparseType.FP32,
-                 output_dtype: SparseType = SparseType.FP32, device="cuda"):
+                 output_dtype: SparseType = SparseType.FP32, device="cuda",
+                 weights_dev: Optional[torch.Tensor] = None,
+                 momentum1_dev: Optional[torch.Tensor] = None):
+        """weights_dev / momentum1_dev: adopt existing flat buffers (tables too large to hold twice)
+        instead of allocating and initialising new ones; they are updated in place."""
         super().__init__()
         load_torch_ops()
         if weights_precision not in (SparseType.FP32, SparseType.FP16):
@@ -70,18 +74,25 @@ class SplitTableBatchedEmbeddingBagsCodegen(torch.nn.Module):
             d_off.append(d_off[-1] + dim)
         self.total_D, self.max_D = d_off[-1], max(d for _, d in self.embedding_specs)
         self.total_hash_size_bits = max(1, (rows_total - 1).bit_length())
-        self.weights_dev = torch.nn.Parameter(torch.empty(pos, dtype=wdtype, device=dev), requires_grad=False)
+        if weights_dev is not None and (weights_dev.numel() != pos or weights_dev.dtype != wdtype):
+            raise ValueError("weights_dev must hold %d %s elements" % (pos, wdtype))
+        self.weights_dev = torch.nn.Parameter(
+            weights_dev if weights_dev is not None else torch.empty(pos, dtype=wdtype, device=dev),
+            requires_grad=False)
         self.register_buffer("weights_offsets", torch.tensor(w_off, dtype=torch.int64, device=dev))
         self.register_buffer("D_offsets", torch.tensor(d_off, dtype=torch.int32, device=dev))
         self.register_buffer("hash_size_cumsum", torch.tensor(h_cum, dtype=torch.int64, device=dev))
-        self.register_buffer("momentum1_dev", torch.zeros(
+        if momentum1_dev is not None and (momentum1_dev.numel() != rows_total or momentum1_dev.dtype != torch.float32):
+            raise ValueError("momentum1_dev must hold %d float32 elements" % rows_total)
+        self.register_buffer("momentum1_dev", momentum1_dev if momentum1_dev is not None else torch.zeros(
             rows_total if optimizer == OptimType.EXACT_ROWWISE_ADAGRAD else 0, dtype=torch.float32, device=dev))
         self.register_buffer("momentum1_offsets", torch.tensor(h_cum[:-1], dtype=torch.int64, device=dev))
         self.register_buffer("_placeholder", torch.zeros(1, device=dev))
         self._empty_w = torch.empty(0, dtype=wdtype, device=dev)
         self._empty_f = torch.empty(0, dtype=torch.float32, device=dev)
         self._empty_i = torch.empty(0, dtype=torch.int32, device=dev)
-        self.init_embedding_weights_uniform(-0.01, 0.01)
+        if weights_dev is None:
+            self.init_embedding_weights_uniform(-0.01, 0.01)
 
     @torch.no_grad()
     def init_embedding_weights_uniform(self, lo: float, hi: float) -> None:
