@@ -289,6 +289,50 @@ def nv12_lib():
     return _nv12
 
 
+def nv12_all_triples(fullrange: bool = False) -> np.ndarray:
+    """RGB of every (y, u, v) triple: uint8 [256, 256, 256, 3]."""
+    out = np.zeros((256, 256, 256, 3), dtype=np.uint8)
+    lib = nv12_lib()
+    lib.nv12_oracle_all_triples.restype = None
+    lib.nv12_oracle_all_triples.argtypes = [ctypes.c_int, ctypes.c_void_p]
+    lib.nv12_oracle_all_triples(int(fullrange), _ptr(out))
+    return out
+
+
+class Nv12Reference:
+    """The reference's ColorConversionKernel.cpp compiled for the host (oracle/_ref, built by
+    oracle/build.py where the reference tree is present). contracted=True: the build that lets the
+    compiler fuse the dot products' multiply-adds."""
+
+    def __init__(self, contracted: bool = False):
+        libs = _build.build_nv12_reference()
+        name = "nv12_ref_fma" if contracted else "nv12_ref"
+        if name not in libs:
+            raise FileNotFoundError("oracle/_ref/lib%s.so is not built (no reference tree here)" % name)
+        self.lib = ctypes.CDLL(libs[name])
+        self.lib.nv12_ref_tile_offset.restype = ctypes.c_size_t
+        self.lib.nv12_ref_tile_offset.argtypes = [ctypes.c_int] * 3
+        self.lib.nv12_ref_all_triples.restype = None
+        self.lib.nv12_ref_all_triples.argtypes = [ctypes.c_int, ctypes.c_void_p]
+        self.lib.nv12_ref_convert.restype = None
+        self.lib.nv12_ref_convert.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_int] * 4
+
+    def tile_offset(self, x: int, y: int, stride: int) -> int:
+        return int(self.lib.nv12_ref_tile_offset(x, y, stride))
+
+    def all_triples(self, fullrange: bool = False) -> np.ndarray:
+        out = np.zeros((256, 256, 256, 3), dtype=np.uint8)
+        self.lib.nv12_ref_all_triples(int(fullrange), _ptr(out))
+        return out
+
+    def convert(self, y_plane, uv_plane, width, height, stride, fullrange=False) -> np.ndarray:
+        y_plane = np.ascontiguousarray(y_plane, dtype=np.uint8)
+        uv_plane = np.ascontiguousarray(uv_plane, dtype=np.uint8)
+        rgb = np.zeros((height, width, 3), dtype=np.uint8)
+        self.lib.nv12_ref_convert(_ptr(y_plane), _ptr(uv_plane), _ptr(rgb), width, height, stride, int(fullrange))
+        return rgb
+
+
 def nv12_offset(x: int, y: int, stride: int, tiled: bool) -> int:
     return int(nv12_lib().nv12_oracle_offset(x, y, stride, int(tiled)))
 

@@ -15,8 +15,11 @@
  *               packed at 3 * (y * width + x)
  *
  * Pin: the reference holds no test vectors for this kernel (its tests compare decoded frames by
- * PSNR against a CPU decoder that is not in the repository), so the pins are known answers of
- * BT.709 itself (tests/test_nv12.py): black, white, mid grey and the primaries.
+ * PSNR against a CPU decoder that is not in the repository). The pins are (tests/test_nv12.py):
+ * the reference's OWN source file compiled for the host (oracle/nv12_ref_wrap.cpp ->
+ * oracle/_ref/libnv12_ref.so) -- its get_tile_offset over every byte of multi-tile surfaces, its
+ * yuv2rgb over all 2^24 (y, u, v) triples in both range modes, its whole kernel over random Tile-Y
+ * frames, all bit for bit -- and known answers of BT.709 itself: black, white, mid grey, primaries.
  *
  * The dot product is evaluated left to right, s0*m0 + s1*m1 + s2*m2, each product and sum rounded
  * to fp32; the CUDA kernel spells the same sequence with __fmul_rn / __fadd_rn. */
@@ -71,6 +74,15 @@ ORACLE_API void nv12_oracle_pixel(uint8_t y, uint8_t u, uint8_t v, int fullrange
     d = d + s2 * kBt709[c][2];
     rgb[c] = to_byte(d);
   }
+}
+
+/* out[3 * ((y << 16) | (u << 8) | v) ...] = RGB of the triple, for all 2^24 triples. */
+ORACLE_API void nv12_oracle_all_triples(int fullrange, uint8_t* out) {
+  for (int y = 0; y < 256; ++y)
+    for (int u = 0; u < 256; ++u)
+      for (int v = 0; v < 256; ++v)
+        nv12_oracle_pixel((uint8_t)y, (uint8_t)u, (uint8_t)v, fullrange,
+                          out + 3 * (((size_t)y << 16) | ((size_t)u << 8) | (size_t)v));
 }
 
 ORACLE_API void nv12_oracle_convert(const uint8_t* y_plane, const uint8_t* uv_plane, uint8_t* rgb,

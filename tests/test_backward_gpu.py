@@ -184,6 +184,7 @@ def test_backward_many_tables_runs_across_spans_and_tiles(gdtype, rows_hint):
     T, B = 30, 900
     rows = [int(r) for r in rng.integers(1, 3000, size=T)]
     Ds = [int(d) for d in rng.choice([4, 8, 16, 32, 64, 100, 128], size=T)]
+    Ds[-1] += (-sum(Ds)) % 8                  # rows of the fp16 gradient matrix are whole 16-byte vectors
     W, wo, Do = helpers.float_tables(rng, rows, Ds, np.float16, -0.5, 0.5)
     lengths = rng.integers(0, 60, size=T * B, dtype=np.int64)
     for t in (3, 4, 17):                       # tables nobody looks up
@@ -216,6 +217,7 @@ def test_backward_run_of_only_bad_indices_leaves_row_zero_alone():
     mom[:] = 0
     a, b = int(offsets[0]), int(offsets[B])
     indices[a:b][indices[a:b] == 0] = 1          # nobody looks up row 0 of table 0 ...
+    indices[a + 3] = 1                            # (row 1 keeps at least one valid lookup)
     bad = indices.copy()
     bad[a:a + 3] = [50, 77, -1]                   # ... except three ids that are out of range
     keep = np.ones(indices.size, dtype=np.float32)

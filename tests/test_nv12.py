@@ -1,14 +1,62 @@
-"""NV12 -> RGB24 oracle (CPU): known answers of BT.709 and the Tile-Y address map.
+"""NV12 -> RGB24 oracle (CPU) pinned to the reference's own kernel source and to BT.709.
 
 The reference holds no vectors for its colour-conversion kernel
-(packages/torchcodec-xpu/src/torchcodec_xpu/ColorConversionKernel.cpp); what pins the restatement
-is the standard itself: limited-range black / white / grey and the 100 % primaries, and for the tiled
-layout the properties the reference's address function has (a bijection of every 4 KB tile onto
-itself, 16-byte columns kept contiguous)."""
+(packages/torchcodec-xpu/src/torchcodec_xpu/ColorConversionKernel.cpp), but the file itself compiles
+for the host on top of a stand-in for the SYCL names it uses (oracle/nv12_ref_wrap.cpp ->
+oracle/_ref/libnv12_ref.so, built where the reference tree is present and carried along as a built
+file). The restatement is compared with it bit for bit: get_tile_offset over every byte of multi-tile
+surfaces, yuv2rgb over all 2^24 triples, the whole kernel over random Tile-Y frames. Beside that:
+known answers of the standard (limited-range black / white / grey, the 100 % primaries) and the
+structural properties of the tiled layout."""
 import numpy as np
 import pytest
 
 import oracle
+from oracle import build as oracle_build
+
+
+def _reference(contracted=False):
+    if not oracle_build.build_nv12_reference():
+        pytest.skip("oracle/_ref is not built and the reference tree is not here")
+    return oracle.Nv12Reference(contracted)
+
+
+@pytest.mark.parametrize("stride,rows", [(256, 64), (384, 96), (128, 32), (1920 + 128, 64)])
+def test_tile_y_offsets_equal_the_references_get_tile_offset(stride, rows):
+    """Every (x, y) of surfaces of 1 x 1, 2 x 2, 3 x 3 and 16 x 2 tiles (ColorConversionKernel.cpp:29-80)."""
+    ref = _reference()
+    for y in range(rows):
+        for x in range(0, stride):
+            assert oracle.nv12_offset(x, y, stride, True) == ref.tile_offset(x, y, stride), (x, y)
+
+
+@pytest.mark.parametrize("fullrange", [False, True])
+def test_every_yuv_triple_equals_the_references_yuv2rgb(fullrange):
+    """All 2^24 triples (ColorConversionKernel.cpp:82-100), and what fusing the dot products'
+    multiply-adds (which a device compiler may do with sycl::dot) would change."""
+    ours = oracle.nv12_all_triples(fullrange)
+    ref = _reference().all_triples(fullrange)
+    assert np.array_equal(ours, ref)
+    fused = _reference(contracted=True).all_triples(fullrange)
+    differ = np.any(fused != ref, axis=-1)
+    # contraction changes the last bit of a few products; after x255 and truncation that moves a
+    # channel by at most one step, for a small share of the triples
+    assert np.abs(fused.astype(np.int16) - ref.astype(np.int16)).max() <= 1
+    assert differ.mean() < 0.05, differ.mean()
+
+
+@pytest.mark.parametrize("fullrange", [False, True])
+def test_whole_frames_equal_the_references_kernel(fullrange):
+    """convertNV12ToRGB (ColorConversionKernel.cpp:131-181) over a random Tile-Y surface whose width
+    and height are not multiples of the tile."""
+    ref = _reference()
+    rng = np.random.default_rng(5)
+    w, h, stride = 300, 70, 384
+    yp = rng.integers(0, 256, size=(96, stride), dtype=np.uint8)      # plane heights padded to 32 rows
+    uv = rng.integers(0, 256, size=(64, stride), dtype=np.uint8)
+    want = ref.convert(yp, uv, w, h, stride, fullrange)
+    got = oracle.nv12_to_rgb(yp, uv, w, h, stride, fullrange, tiled=True)
+    assert np.array_equal(got, want)
 
 
 @pytest.mark.parametrize("yuv,rgb", [

@@ -20,10 +20,6 @@
 //               a second kernel streams each chunk into a partial row in scratch and a third adds a
 //               run's partials in chunk order and applies the update.
 // Summation order is fixed by the data alone on both paths.
-#include <stdlib.h>
-
-#include <type_traits>
-
 #include "radix_sort.cuh"
 #include "scan.cuh"
 #include "tbe_bags.cuh"
@@ -39,18 +35,11 @@ constexpr int kSegItems = 4;
 constexpr int kSegTile = kSegThreads * kSegItems;
 constexpr uint32_t kInvalidPayload = 0xffffffffu;
 
-inline int env_int(const char* name) {
-  const char* e = getenv(name);
-  return e ? atoi(e) : 0;
-}
-inline int sweep_tune_ctas() { return env_int("B200TBE_SWEEP_CTAS"); }
-inline int sweep_tune_l1() { return env_int("B200TBE_SWEEP_L1"); }
-
-// Widest digit of the segmented sort's passes.
-inline int sweep_digit_bits() {
-  const int v = env_int("B200TBE_SORT_DIGIT_BITS");
-  return v >= 4 && v <= 11 ? v : 11;
-}
+// Widest digit of the segmented sort's passes: 8 bits (22-bit row ids sort in passes of 8, 7 and
+// 7 bits). Measured on the bench step against two passes of 11 bits: the 256-digit scatter runs at
+// 0.68 ms per pass, the 2048-digit one at 1.57 ms (its digit tables leave three CTAs per SM and the
+// per-tile digit scan is eight times as long).
+constexpr int kSweepSortDigitBits = 8;
 
 struct BwdDev {
   char* dev_weights;
@@ -91,7 +80,6 @@ struct BwdDev {
   const uint32_t* total_tiles;     // tiles in use
   const uint4* tile_desc;          // [max_tiles] {begin, count, table, first tile of the table}
   uint32_t* span_flags;            // [max_tiles * 16]
-  int32_t tune_prefetch_l1;        // experiment switch
 };
 
 // ---- linearize -----------------------------------------------------------------------------
@@ -905,18 +893,8 @@ int launch_sweep(const BwdDev& d, int max_tiles, cudaStream_t stream) {
   const int64_t ctas = static_cast<int64_t>(max_tiles) * (kSpansPerTile / kSpansPerCta);
   const int64_t spans = static_cast<int64_t>(max_tiles) * kSpansPerTile;
   if (ctas > 0x7fffffff || spans / kSweepWarps > 0x7fffffff) return B200TBE_ERR_TOO_LARGE;
-  const int tune = sweep_tune_ctas();
-  if (std::is_same<WT, __half>::value && std::is_same<GT, __half>::value && !kScaled && GS == 16 && tune != 0) {
-    if (tune == 6)
-      sweep_runs_kernel<__half, __half, false, 16, 2, 6><<<static_cast<unsigned>(ctas), kSweepThreads, 0, stream>>>(d);
-    else if (tune == 10)
-      sweep_runs_kernel<__half, __half, false, 16, 2, 10><<<static_cast<unsigned>(ctas), kSweepThreads, 0, stream>>>(d);
-    else
-      sweep_runs_kernel<__half, __half, false, 16, 2, 5><<<static_cast<unsigned>(ctas), kSweepThreads, 0, stream>>>(d);
-  } else {
-    sweep_runs_kernel<WT, GT, kScaled, GS, kC, sweep_ctas_per_sm<GT, kC>()>
-        <<<static_cast<unsigned>(ctas), kSweepThreads, 0, stream>>>(d);
-  }
+  sweep_runs_kernel<WT, GT, kScaled, GS, kC, sweep_ctas_per_sm<WT, GT, kC>()>
+      <<<static_cast<unsigned>(ctas), kSweepThreads, 0, stream>>>(d);
   finish_open_runs_kernel<WT, GS, kC>
       <<<static_cast<unsigned>(spans / kSweepWarps), kSweepThreads, 0, stream>>>(d);
   return launch_status();
@@ -924,9 +902,11 @@ int launch_sweep(const BwdDev& d, int max_tiles, cudaStream_t stream) {
 
 template <typename WT, typename GT, bool kScaled>
 int dispatch_sweep_shape(const BwdDev& d, int max_tiles, cudaStream_t stream) {
-  // lanes per row x quads per lane: the smallest group that holds max_D elements
-  if (d.max_D <= 64) return launch_sweep<WT, GT, kScaled, 8, 2>(d, max_tiles, stream);
-  if (d.max_D <= 128) return launch_sweep<WT, GT, kScaled, 16, 2>(d, max_tiles, stream);
+  // lanes per row x quads per lane: rows of up to 128 elements get one quad per lane of the
+  // smallest group that holds them, wider rows the whole warp with several quads per lane
+  if (d.max_D <= 32) return launch_sweep<WT, GT, kScaled, 8, 1>(d, max_tiles, stream);
+  if (d.max_D <= 64) return launch_sweep<WT, GT, kScaled, 16, 1>(d, max_tiles, stream);
+  if (d.max_D <= 128) return launch_sweep<WT, GT, kScaled, 32, 1>(d, max_tiles, stream);
   if (d.max_D <= 256) return launch_sweep<WT, GT, kScaled, 32, 2>(d, max_tiles, stream);
   return launch_sweep<WT, GT, kScaled, 32, 4>(d, max_tiles, stream);
 }
@@ -977,7 +957,7 @@ int run_backward_sweep(BwdDev d, const b200tbe_backward_params* p, const Scratch
         <<<static_cast<unsigned>(lin_ctas), kBwdThreads, 0, stream>>>(d, key_bits, keys_a, vals_a);
   }
   bool in_b = false;
-  st = radix_sort_pairs_planned(keys_a, vals_a, keys_b, vals_b, n, key_bits, sweep_digit_bits(),
+  st = radix_sort_pairs_planned(keys_a, vals_a, keys_b, vals_b, n, key_bits, kSweepSortDigitBits,
                                           plan, scratch + L.sort, radix_sort_planned_scratch_bytes(max_tiles),
                                           &in_b, stream);
   if (st != B200TBE_OK) return st;
@@ -1075,7 +1055,6 @@ extern "C" int b200tbe_backward(const b200tbe_backward_params* p, b200tbe_stream
   d.counters = reinterpret_cast<uint32_t*>(scratch + L.counters);
   d.partials = reinterpret_cast<float*>(scratch + L.partials);
   d.max_D = p->max_D;
-  d.tune_prefetch_l1 = sweep_tune_l1();
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   const bool i64 = p->index_bytes == 8;
   if (L.sweep)

@@ -14,6 +14,11 @@
 //     weight row of every run that ends in the batch -- one batch ahead of its use;
 //   * per position: the slice offset arrives by shuffle, four positions' loads are issued before the
 //     first is added, and where a run ends the row is updated once, in place ("exact" update);
+//   * three rows in four are looked up once. Where a warp carries several groups, updating such a
+//     run inside the sweep would run the whole update sequence for one group while the others
+//     idle, so the batch's one-lookup runs are left out of the sweep and updated in a pass of their
+//     own, one per GROUP and step whichever span they lie in. Rows of 128 elements and more take the
+//     whole warp (one group), where every update is full width anyway;
 //   * a run that crosses a span boundary leaves partial sums in scratch instead (the piece that
 //     ends a run begun earlier -> "head" slot of the span, the piece that begins a run finished
 //     later -> "tail" slot); finish_open_runs_kernel adds a run's pieces in span order and updates.
@@ -31,9 +36,15 @@ template <int kC>
 __host__ __device__ constexpr int sweep_loads() {
   return kC <= 2 ? 4 : 2;
 }
-template <typename GT, int kC>
+// one fp16 quad per lane of gradient and of weights costs two registers each per position: eight
+// positions in flight; anything wider, four (or two)
+template <typename WT, typename GT, bool kScaled, int kC>
+__host__ __device__ constexpr int sweep_loads_for() {
+  return kC == 1 && sizeof(GT) == 2 && sizeof(WT) == 2 && !kScaled ? 8 : sweep_loads<kC>();
+}
+template <typename WT, typename GT, int kC>
 __host__ __device__ constexpr int sweep_ctas_per_sm() {
-  return kC > 2 ? 5 : 8;
+  return kC > 2 ? 4 : (kC == 2 ? (sizeof(WT) == 2 && sizeof(GT) == 2 ? 5 : 4) : 6);
 }
 constexpr uint32_t kNoSlice = 0xffffffffu;
 constexpr uint32_t kSpanTailOwner = 1u;   // the span's last run continues to the right; its piece is in the tail slot
@@ -179,11 +190,11 @@ __device__ __forceinline__ SweepTable<WT, GT> sweep_table(const BwdDev& p, int t
 template <typename WT, int kC>
 __device__ __forceinline__ void sweep_update(const BwdDev& p, const float4 (&acc)[kC],
                                              const typename Quad<WT>::Raw (&wv)[kC], const bool (&on)[kC],
-                                             float sq, float m_old, float* mptr, char* wrow, int D,
+                                             float sq, float m_old, float* mptr, char* wrow, float inv_D,
                                              int quad_w, bool write, bool first_lane) {
   float step = p.learning_rate;
   if (p.optimizer == B200TBE_OPT_ROWWISE_ADAGRAD) {
-    const float m_new = m_old + sq / static_cast<float>(D);
+    const float m_new = fmaf(sq, inv_D, m_old);   // m += mean of the squares
     if (write && first_lane) *mptr = m_new;
     step = __fdividef(p.learning_rate, sqrt_fast(m_new) + p.eps);
   }
@@ -225,49 +236,37 @@ struct SweepMeta {
   uint32_t row;    // row id of the position
   uint32_t goff;   // offset of its gradient slice in 16-byte units, kNoSlice for a skipped lookup
   float mult;      // factor of the slice (per-sample weight, 1 / bag length)
-  bool tail;       // the position ends a run
+  bool tail;       // the position ends a run of several lookups
+  bool single;     // the position is a whole run: the row's only lookup
 };
 
-template <typename WT, typename GT, bool kScaled, int GS, int kC, int kMinCtas>
-__global__ void __launch_bounds__(kSweepThreads, kMinCtas)
-    sweep_runs_kernel(const __grid_constant__ BwdDev p) {
+// Where a group's span lies (per lane; spans of one warp are consecutive and share the table).
+struct SpanCtx {
+  uint32_t span_id;
+  uint32_t s_begin;     // first sorted position of the span
+  int s_count;          // positions in the span (0: this group has none)
+  int cnt0;             // positions in the warp's first span (the longest of the warp)
+  uint32_t seg_begin, seg_end;   // the table's sorted positions
+  int grp, gl;
+};
+
+// kFull: the table's rows fill the group exactly (D = GS * kC * 4), so no lane ever sits out.
+template <typename WT, typename GT, bool kScaled, int GS, int kC, bool kFull, int kSweepLoads>
+__device__ __forceinline__ void sweep_span(const BwdDev& p, const SpanCtx& sc, const SweepTable<WT, GT>& tab) {
   constexpr int NG = 32 / GS;
-  constexpr int kSweepLoads = sweep_loads<kC>();
-  constexpr int kSpansPerCta = kSweepWarps * NG;
-  static_assert(kSpansPerTile % kSpansPerCta == 0, "a CTA's spans lie in one tile");
-  constexpr int kCtasPerTile = kSpansPerTile / kSpansPerCta;
   constexpr uint32_t kGroupBits = GS == 32 ? 1u : (GS == 16 ? 0x00010001u : 0x01010101u);
+  constexpr uint32_t kBlockBits = kGroupBits * ((1u << kSweepLoads) - 1u);
   constexpr int quad_w = GS * 4 * static_cast<int>(sizeof(WT));   // bytes between a lane's quads
   constexpr int quad_g = GS * 4 * static_cast<int>(sizeof(GT));
-
-  const uint32_t tile = blockIdx.x / kCtasPerTile;
-  if (tile >= __ldg(p.total_tiles)) return;
-  const uint4 td = __ldg(p.tile_desc + tile);   // {begin, count, table, first tile of the table}
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int grp = lane / GS, gl = lane % GS;
-  const int warp_span0 = static_cast<int>(blockIdx.x % kCtasPerTile) * kSpansPerCta + warp * NG;
-  const int tile_n = static_cast<int>(td.y);
-  if (warp_span0 * kSpan >= tile_n) return;
-  const int span_in_tile = warp_span0 + grp;
-  const uint32_t span_id = tile * kSpansPerTile + span_in_tile;
-  const int t = static_cast<int>(td.z);
-  const int s_off = span_in_tile * kSpan;
-  const int s_count = s_off >= tile_n ? 0 : (tile_n - s_off < kSpan ? tile_n - s_off : kSpan);
-  const int cnt0 = tile_n - warp_span0 * kSpan < kSpan ? tile_n - warp_span0 * kSpan : kSpan;  // group 0: the longest
-  const uint32_t s_begin = td.x + s_off;
-  const uint32_t seg_begin = __ldg(p.seg_start + t), seg_end = __ldg(p.seg_start + t + 1);
+  const int grp = sc.grp, gl = sc.gl;
+  const uint32_t s_begin = sc.s_begin, seg_begin = sc.seg_begin, seg_end = sc.seg_end;
+  const int s_count = sc.s_count, cnt0 = sc.cnt0;
   const uint32_t* __restrict__ keys = reinterpret_cast<const uint32_t*>(p.sorted_keys);
   const uint32_t* __restrict__ vals = p.sorted_vals;
 
-  const SweepTable<WT, GT> tab = sweep_table<WT, GT, GS, kC>(p, t, gl);
-  if (!tab.ok) {
-    if (lane == 0 && p.status != nullptr) atomicOr(p.status, B200TBE_DEV_UNSUPPORTED_SHAPE);
-    if (gl == 0 && s_count > 0) p.span_flags[span_id] = 0;
-    return;
-  }
   bool on[kC];
 #pragma unroll
-  for (int c = 0; c < kC; ++c) on[c] = (c * GS + gl) * 4 < tab.D;
+  for (int c = 0; c < kC; ++c) on[c] = kFull || (c * GS + gl) * 4 < tab.D;
 
   // does the span begin inside a run, does it end inside one?
   bool first_pending = false, tail_open = false;
@@ -277,73 +276,151 @@ __global__ void __launch_bounds__(kSweepThreads, kMinCtas)
     if (last + 1 < seg_end) tail_open = __ldg(keys + last) == __ldg(keys + last + 1);
   }
 
-  auto load_meta = [&](int b) {
+  const uint32_t gstride16 = static_cast<uint32_t>(tab.gstride_bytes >> 4);
+  const char* w_row0 = tab.w_lane - gl * 4 * static_cast<int>(sizeof(WT));
+  const float inv_D = 1.f / static_cast<float>(tab.D);
+
+  // Three batches are in the pipe: the ids and bag ids of batch b + 2 are being loaded, batch
+  // b + 1 is being turned into slice offsets (and the rows of the runs that end in it are asked
+  // from L2), batch b is being summed. No step waits on a load issued in the same step.
+  struct Raw {
+    uint32_t key, next, prev, payload;
+  };
+  auto load_raw = [&](int b) {
+    Raw r;
+    const int i = b + gl;
+    const uint32_t pos = s_begin + i;
+    r.key = 0;
+    r.next = 0xffffffffu;
+    r.prev = 0xffffffffu;
+    r.payload = kInvalidPayload;
+    if (i < s_count) {
+      r.key = __ldg(keys + pos);
+      if (pos + 1 < seg_end) r.next = __ldg(keys + pos + 1);
+      if (pos > seg_begin) r.prev = __ldg(keys + pos - 1);
+      r.payload = __ldg(vals + pos);
+    }
+    return r;
+  };
+  auto derive = [&](const Raw& r, int b) {
     SweepMeta m;
     const int i = b + gl;
     const bool valid = i < s_count;
     const uint32_t pos = s_begin + i;
-    m.row = 0;
+    m.row = r.key;
     m.goff = kNoSlice;
     m.mult = 1.f;
-    m.tail = false;
-    if (valid) {
-      m.row = __ldg(keys + pos);
-      const bool last_of_table = pos + 1 >= seg_end;
-      const uint32_t next = last_of_table ? 0u : __ldg(keys + pos + 1);
-      m.tail = last_of_table || next != m.row;
-      const uint32_t payload = __ldg(vals + pos);
-      if (payload != kInvalidPayload) {
-        int64_t bag = payload;
-        if (kScaled) {
-          if (p.per_sample_weights != nullptr) {
-            m.mult = __ldg(p.per_sample_weights + payload);
-            bag = __ldg(p.bag_of_pos + payload);
-          }
-          if (p.pooling_mode == B200TBE_POOL_MEAN) m.mult /= static_cast<float>(bag_length(p, bag));
+    // the table's first / last position begins / ends a run whatever lies beside it in memory
+    const bool ends = valid && (pos + 1 >= seg_end || r.next != r.key);
+    const bool begins = valid && (pos <= seg_begin || r.prev != r.key);
+    if (valid && r.payload != kInvalidPayload) {
+      int64_t bag = r.payload;
+      if (kScaled) {
+        if (p.per_sample_weights != nullptr) {
+          m.mult = __ldg(p.per_sample_weights + r.payload);
+          bag = __ldg(p.bag_of_pos + r.payload);
         }
-        m.goff = static_cast<uint32_t>(((bag - tab.bag0) * tab.gstride_bytes) >> 4);
+        if (p.pooling_mode == B200TBE_POOL_MEAN) m.mult /= static_cast<float>(bag_length(p, bag));
       }
-      if (m.tail) {
-        // the row's weights and state start their way from HBM now, a batch ahead of the update
-        const char* w = tab.w_lane - gl * 4 * static_cast<int>(sizeof(WT)) +
-                        static_cast<uint64_t>(m.row) * static_cast<uint32_t>(tab.row_bytes);
-        if (p.tune_prefetch_l1) {
-          for (int off = 0; off < tab.row_bytes; off += 128)
-            asm volatile("prefetch.global.L1 [%0];" ::"l"(w + off));
-          if (tab.mbase != nullptr) asm volatile("prefetch.global.L1 [%0];" ::"l"(tab.mbase + m.row));
-        } else {
-          for (int off = 0; off < tab.row_bytes; off += 128)
-            asm volatile("prefetch.global.L2 [%0];" ::"l"(w + off));
-          if (tab.mbase != nullptr) asm volatile("prefetch.global.L2 [%0];" ::"l"(tab.mbase + m.row));
-        }
-      }
+      m.goff = static_cast<uint32_t>((bag - tab.bag0) * gstride16);
+    }
+    // a run of one lookup needs no summing: it is updated in the singles pass of its batch (a
+    // skipped lookup that is alone on its row needs nothing at all)
+    m.single = NG > 1 && begins && ends && m.goff != kNoSlice;
+    m.tail = ends && !m.single && (NG == 1 || !begins);
+    if (m.single || m.tail) {
+      // the row's weights and state start their way from HBM now, a batch ahead of the update
+      const char* w = w_row0 + static_cast<uint64_t>(m.row) * static_cast<uint32_t>(tab.row_bytes);
+      for (int off = 0; off < tab.row_bytes; off += 128)
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(w + off));
+      if (tab.mbase != nullptr) asm volatile("prefetch.global.L2 [%0];" ::"l"(tab.mbase + m.row));
     }
     return m;
   };
-
   float4 acc[kC];
 #pragma unroll
   for (int c = 0; c < kC; ++c) acc[c] = make_float4(0.f, 0.f, 0.f, 0.f);
 
-  SweepMeta cur = load_meta(0);
+  SweepMeta cur = derive(load_raw(0), 0);
+  Raw raw1 = load_raw(GS);
   for (int b = 0; b < cnt0; b += GS) {
-    const SweepMeta nxt = load_meta(b + GS);
+    const Raw raw2 = load_raw(b + 2 * GS);
+    const SweepMeta nxt = derive(raw1, b + GS);
     const uint32_t tailmask = __ballot_sync(kFullMask, cur.tail);
+    // positions the sweep has to visit: lookups of runs of several lookups
+    const uint32_t goff_sweep = cur.single ? kNoSlice : cur.goff;
+    const uint32_t sliced = __ballot_sync(kFullMask, goff_sweep != kNoSlice);
+    const uint32_t work = sliced | tailmask;
     const int nsteps = cnt0 - b < GS ? cnt0 - b : GS;
     for (int j0 = 0; j0 < nsteps; j0 += kSweepLoads) {
+      if (((work >> j0) & kBlockBits) == 0) continue;   // nothing but one-lookup runs here
+      // gradient slices of the next kSweepLoads positions: all requested before the first is added.
+      // The usual block -- every position of every group has a slice -- loads without a test.
       typename Quad<GT>::Raw x[kSweepLoads][kC];
       float mu[kSweepLoads];
+      const bool all_sliced = kFull && ((~sliced >> j0) & kBlockBits) == 0;
+      if (all_sliced) {
+#pragma unroll
+        for (int u = 0; u < kSweepLoads; ++u) {
+          const uint32_t off = __shfl_sync(kFullMask, goff_sweep, j0 + u, GS);   // j0 + u < GS
+          mu[u] = 1.f;
+          if (kScaled) mu[u] = __shfl_sync(kFullMask, cur.mult, j0 + u, GS);
+          const char* src = tab.g_lane + (static_cast<uint64_t>(off) << 4);
+#pragma unroll
+          for (int c = 0; c < kC; ++c) x[u][c] = Quad<GT>::load_ro(src + c * quad_g);
+        }
+      } else {
+#pragma unroll
+        for (int u = 0; u < kSweepLoads; ++u) {
+          const uint32_t off = __shfl_sync(kFullMask, goff_sweep, j0 + u, GS);
+          mu[u] = 1.f;
+          if (kScaled) mu[u] = __shfl_sync(kFullMask, cur.mult, j0 + u, GS);
+          const char* src = tab.g_lane + (static_cast<uint64_t>(off) << 4);
+#pragma unroll
+          for (int c = 0; c < kC; ++c) {
+            x[u][c] = Quad<GT>::zero();
+            if (off != kNoSlice && on[c]) x[u][c] = Quad<GT>::load_ro(src + c * quad_g);
+          }
+        }
+      }
+      if (((tailmask >> j0) & kBlockBits) == 0) {
+        // no run of any group ends among these positions (always so inside a long run): just add
+#pragma unroll
+        for (int u = 0; u < kSweepLoads; ++u) {
+#pragma unroll
+          for (int c = 0; c < kC; ++c) {
+            if (kScaled) {
+              const float4 f = Quad<GT>::to(x[u][c]);
+              acc[c].x = fmaf(f.x, mu[u], acc[c].x);
+              acc[c].y = fmaf(f.y, mu[u], acc[c].y);
+              acc[c].z = fmaf(f.z, mu[u], acc[c].z);
+              acc[c].w = fmaf(f.w, mu[u], acc[c].w);
+            } else {
+              Quad<GT>::add(acc[c], x[u][c]);
+            }
+          }
+        }
+        continue;
+      }
+      // every run of this group that ends among these positions: its row's weights and state are
+      // requested now, so that the updates below wait for one round trip together, not one each
+      typename Quad<WT>::Raw wv[kSweepLoads][kC];
+      float m_old[kSweepLoads];
+      uint32_t rows[kSweepLoads];
 #pragma unroll
       for (int u = 0; u < kSweepLoads; ++u) {
-        const int j = j0 + u;   // < GS: kSweepLoads divides GS
-        const uint32_t off = __shfl_sync(kFullMask, cur.goff, j, GS);
-        mu[u] = 1.f;
-        if (kScaled) mu[u] = __shfl_sync(kFullMask, cur.mult, j, GS);
-        const char* src = tab.g_lane + (static_cast<uint64_t>(off) << 4);
+        rows[u] = 0;
+        m_old[u] = 0.f;
 #pragma unroll
-        for (int c = 0; c < kC; ++c) {
-          x[u][c] = Quad<GT>::zero();
-          if (off != kNoSlice && on[c]) x[u][c] = Quad<GT>::load_ro(src + c * quad_g);
+        for (int c = 0; c < kC; ++c) wv[u][c] = Quad<WT>::zero();
+        if (((tailmask >> (j0 + u)) & kGroupBits) == 0) continue;
+        rows[u] = __shfl_sync(kFullMask, cur.row, j0 + u, GS);
+        if ((tailmask >> (grp * GS + j0 + u)) & 1u) {
+          const char* wrow = tab.w_lane + static_cast<uint64_t>(rows[u]) * static_cast<uint32_t>(tab.row_bytes);
+#pragma unroll
+          for (int c = 0; c < kC; ++c)
+            if (on[c]) wv[u][c] = Quad<WT>::load(wrow + c * quad_w);
+          if (tab.mbase != nullptr) m_old[u] = tab.mbase[rows[u]];
         }
       }
 #pragma unroll
@@ -364,44 +441,141 @@ __global__ void __launch_bounds__(kSweepThreads, kMinCtas)
         if (((tailmask >> j) & kGroupBits) == 0) continue;   // no group's run ends here
         // ---- a run ends at position j of some group ----
         const bool mine = (tailmask >> (grp * GS + j)) & 1u;
-        const uint32_t row = __shfl_sync(kFullMask, cur.row, j, GS);
-        const bool upd = mine && !first_pending;
-        char* wrow = tab.w_lane + static_cast<uint64_t>(row) * static_cast<uint32_t>(tab.row_bytes);
-        typename Quad<WT>::Raw wv[kC];
-        float m_old = 0.f;
-#pragma unroll
-        for (int c = 0; c < kC; ++c) {
-          wv[c] = Quad<WT>::zero();
-          if (upd && on[c]) wv[c] = Quad<WT>::load(wrow + c * quad_w);
-        }
-        if (upd && tab.mbase != nullptr) m_old = tab.mbase[row];
         float sq = sum_squares<kC>(acc);
 #pragma unroll
         for (int o = GS >> 1; o > 0; o >>= 1) sq += __shfl_xor_sync(kFullMask, sq, o);
         if (mine) {
           if (first_pending) {
-            store_partial<kC>(p.partials + static_cast<int64_t>(2 * span_id) * p.max_D, acc, on, gl, GS);
+            store_partial<kC>(p.partials + static_cast<int64_t>(2 * sc.span_id) * p.max_D, acc, on, gl, GS);
             first_pending = false;
           } else if (sq != 0.f) {
             // an all-zero sum (only skipped lookups, or gradients that are zero) leaves the row as it is
-            sweep_update<WT, kC>(p, acc, wv, on, sq, m_old, tab.mbase + row, wrow, tab.D, quad_w, true, gl == 0);
+            char* wrow = tab.w_lane + static_cast<uint64_t>(rows[u]) * static_cast<uint32_t>(tab.row_bytes);
+            sweep_update<WT, kC>(p, acc, wv[u], on, sq, m_old[u], tab.mbase + rows[u], wrow, inv_D, quad_w, true,
+                                 gl == 0);
           }
 #pragma unroll
           for (int c = 0; c < kC; ++c) acc[c] = make_float4(0.f, 0.f, 0.f, 0.f);
         }
       }
     }
+
+    // ---- the batch's runs of one lookup: NG of them per step, one per group, whichever group's span
+    // they lie in (a tile's spans share the table), two steps' loads in flight ----
+    uint32_t singles = __ballot_sync(kFullMask, cur.single);
+    while (singles != 0) {
+      constexpr int kRounds = 2;
+      int from[kRounds];
+#pragma unroll
+      for (int r = 0; r < kRounds; ++r) {
+        from[r] = -1;
+#pragma unroll
+        for (int g = 0; g < NG; ++g) {
+          const int l = __ffs(singles) - 1;   // -1 once the mask is empty
+          singles &= singles - 1;
+          if (g == grp) from[r] = l;
+        }
+      }
+      typename Quad<GT>::Raw x[kRounds][kC];
+      typename Quad<WT>::Raw wv[kRounds][kC];
+      float mu[kRounds], m_old[kRounds];
+      uint32_t rows[kRounds];
+#pragma unroll
+      for (int r = 0; r < kRounds; ++r) {
+        const uint32_t off = __shfl_sync(kFullMask, cur.goff, from[r] & 31);
+        rows[r] = __shfl_sync(kFullMask, cur.row, from[r] & 31);
+        mu[r] = 1.f;
+        if (kScaled) mu[r] = __shfl_sync(kFullMask, cur.mult, from[r] & 31);
+        m_old[r] = 0.f;
+        const char* src = tab.g_lane + (static_cast<uint64_t>(off) << 4);
+        const char* wrow = tab.w_lane + static_cast<uint64_t>(rows[r]) * static_cast<uint32_t>(tab.row_bytes);
+#pragma unroll
+        for (int c = 0; c < kC; ++c) {
+          x[r][c] = Quad<GT>::zero();
+          wv[r][c] = Quad<WT>::zero();
+          if (from[r] >= 0 && on[c]) {
+            x[r][c] = Quad<GT>::load_ro(src + c * quad_g);
+            wv[r][c] = Quad<WT>::load(wrow + c * quad_w);
+          }
+        }
+        if (from[r] >= 0 && tab.mbase != nullptr) m_old[r] = tab.mbase[rows[r]];
+      }
+#pragma unroll
+      for (int r = 0; r < kRounds; ++r) {
+        float4 g1[kC];
+#pragma unroll
+        for (int c = 0; c < kC; ++c) {
+          g1[c] = Quad<GT>::to(x[r][c]);
+          if (kScaled) {
+            g1[c].x *= mu[r];
+            g1[c].y *= mu[r];
+            g1[c].z *= mu[r];
+            g1[c].w *= mu[r];
+          }
+        }
+        float sq = sum_squares<kC>(g1);
+#pragma unroll
+        for (int o = GS >> 1; o > 0; o >>= 1) sq += __shfl_xor_sync(kFullMask, sq, o);
+        if (from[r] >= 0 && sq != 0.f) {
+          char* wrow = tab.w_lane + static_cast<uint64_t>(rows[r]) * static_cast<uint32_t>(tab.row_bytes);
+          sweep_update<WT, kC>(p, g1, wv[r], on, sq, m_old[r], tab.mbase + rows[r], wrow, inv_D, quad_w, true,
+                               gl == 0);
+        }
+      }
+    }
     cur = nxt;
+    raw1 = raw2;
   }
 
   if (s_count > 0) {
     uint32_t flags = 0;
     if (tail_open) {
       flags = first_pending ? kSpanThrough : kSpanTailOwner;
-      float* dst = p.partials + static_cast<int64_t>(2 * span_id + (first_pending ? 0 : 1)) * p.max_D;
+      float* dst = p.partials + static_cast<int64_t>(2 * sc.span_id + (first_pending ? 0 : 1)) * p.max_D;
       store_partial<kC>(dst, acc, on, gl, GS);
     }
-    if (gl == 0) p.span_flags[span_id] = flags;
+    if (gl == 0) p.span_flags[sc.span_id] = flags;
+  }
+}
+
+template <typename WT, typename GT, bool kScaled, int GS, int kC, int kMinCtas, int kLoads = sweep_loads_for<WT, GT, kScaled, kC>()>
+__global__ void __launch_bounds__(kSweepThreads, kMinCtas)
+    sweep_runs_kernel(const __grid_constant__ BwdDev p) {
+  constexpr int NG = 32 / GS;
+  constexpr int kSpansPerCta = kSweepWarps * NG;
+  static_assert(kSpansPerTile % kSpansPerCta == 0, "a CTA's spans lie in one tile");
+  constexpr int kCtasPerTile = kSpansPerTile / kSpansPerCta;
+
+  const uint32_t tile = blockIdx.x / kCtasPerTile;
+  if (tile >= __ldg(p.total_tiles)) return;
+  const uint4 td = __ldg(p.tile_desc + tile);   // {begin, count, table, first tile of the table}
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  SpanCtx sc;
+  sc.grp = lane / GS;
+  sc.gl = lane % GS;
+  const int warp_span0 = static_cast<int>(blockIdx.x % kCtasPerTile) * kSpansPerCta + warp * NG;
+  const int tile_n = static_cast<int>(td.y);
+  if (warp_span0 * kSpan >= tile_n) return;
+  const int span_in_tile = warp_span0 + sc.grp;
+  sc.span_id = tile * kSpansPerTile + span_in_tile;
+  const int t = static_cast<int>(td.z);
+  const int s_off = span_in_tile * kSpan;
+  sc.s_count = s_off >= tile_n ? 0 : (tile_n - s_off < kSpan ? tile_n - s_off : kSpan);
+  sc.cnt0 = tile_n - warp_span0 * kSpan < kSpan ? tile_n - warp_span0 * kSpan : kSpan;
+  sc.s_begin = td.x + s_off;
+  sc.seg_begin = __ldg(p.seg_start + t);
+  sc.seg_end = __ldg(p.seg_start + t + 1);
+
+  const SweepTable<WT, GT> tab = sweep_table<WT, GT, GS, kC>(p, t, sc.gl);
+  if (!tab.ok) {
+    if (lane == 0 && p.status != nullptr) atomicOr(p.status, B200TBE_DEV_UNSUPPORTED_SHAPE);
+    if (sc.gl == 0 && sc.s_count > 0) p.span_flags[sc.span_id] = 0;
+    return;
+  }
+  if (tab.D == GS * kC * 4) {
+    sweep_span<WT, GT, kScaled, GS, kC, true, kLoads>(p, sc, tab);
+  } else {
+    sweep_span<WT, GT, kScaled, GS, kC, false, kLoads>(p, sc, tab);
   }
 }
 
@@ -495,5 +669,5 @@ __global__ void __launch_bounds__(kSweepThreads)
     wv[c] = Quad<WT>::zero();
     if (grp == 0 && on[c]) wv[c] = Quad<WT>::load(wrow + c * quad_w);
   }
-  sweep_update<WT, kC>(p, acc, wv, on, sq, m_old, mptr, wrow, D, quad_w, grp == 0, gl == 0);
+  sweep_update<WT, kC>(p, acc, wv, on, sq, m_old, mptr, wrow, 1.f / static_cast<float>(D), quad_w, grp == 0, gl == 0);
 }

@@ -1,0 +1,253 @@
+// Quantised-inference lookup for the common tables: INT8 and INT4 rows of at most 128 elements.
+//
+// One warp per bag in a plain grid, no shared memory. A row is {fp16 scale, fp16 bias} followed by
+// the codes, so the codes start 4 bytes into a 16-byte aligned row: they cannot be fetched with
+// aligned 16-byte vectors without dragging the header and the padding through the arithmetic. They
+// can be fetched as 32-bit words, which is how this kernel reads them: half a warp takes one row,
+// lane w of the half loads code word w (INT8: also word w + 16) and the header word, which all 16
+// lanes read from the same address (one broadcast transaction), so EVERY lane dequantises payload:
+// 8 elements per lane and row for D = 128 in either type. Two rows (one per half-warp) travel
+// through each instruction, several steps' loads are issued before the first is used, and loads
+// allocate in L1, where the head of a skewed id stream stays.
+//
+// Arithmetic per element: the code becomes an exact fp16 integer (byte or nibble dropped into the
+// mantissa of 1024.0, then minus 1024 -- for the nibbles that sit 4 bits up, times 1/16 minus 64),
+// and one mixed-precision fma adds code x scale, both fp16, into the fp32 sum: the product is
+// exact, the sum is rounded once, as in q * scale + bias evaluated in fp32. The biases of a bag's
+// rows are summed once per row and added to every element at the end.
+//
+// Part of tbe_nbit.cu: included there inside its namespace, after NbitParams.
+#pragma once
+
+constexpr int kNbitBagWarps = 8;
+constexpr int kNbitBagThreads = kNbitBagWarps * 32;
+constexpr int kNbitBagCtasPerSm = 6;
+constexpr int kNbitBagMaxD = 128;
+
+// Tables this kernel takes; everything else (INT2, float rows, wider or oddly aligned rows) stays
+// on the ring engine. Both kernels evaluate this, so every table is pooled exactly once.
+__device__ __forceinline__ bool nbit_bag_path(int ty, int D, const char* table, int64_t row_stride) {
+  if (D <= 0 || D > kNbitBagMaxD || (row_stride & 3) != 0 || (reinterpret_cast<uintptr_t>(table) & 3) != 0)
+    return false;
+  if (ty == B200TBE_INT8) return (D & 3) == 0;
+  if (ty == B200TBE_INT4) return (D & 7) == 0;
+  return false;
+}
+
+__device__ __forceinline__ uint32_t ldg_cached4(const void* p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+
+// acc += code (fp16, low or high half of q2) * scale (fp16, low half of hdr), fp32 accumulate.
+__device__ __forceinline__ void fma_code_lo(float& acc, uint32_t q2, uint32_t hdr) {
+  asm("{.reg .f16 ql, qh, s, b;\n"
+      "mov.b32 {ql, qh}, %1;\n"
+      "mov.b32 {s, b}, %2;\n"
+      "fma.rn.f32.f16 %0, ql, s, %0;}\n"
+      : "+f"(acc)
+      : "r"(q2), "r"(hdr));
+}
+__device__ __forceinline__ void fma_code_hi(float& acc, uint32_t q2, uint32_t hdr) {
+  asm("{.reg .f16 ql, qh, s, b;\n"
+      "mov.b32 {ql, qh}, %1;\n"
+      "mov.b32 {s, b}, %2;\n"
+      "fma.rn.f32.f16 %0, qh, s, %0;}\n"
+      : "+f"(acc)
+      : "r"(q2), "r"(hdr));
+}
+// acc += bias (fp16, high half of hdr)
+__device__ __forceinline__ void add_bias(float& acc, uint32_t hdr) {
+  asm("{.reg .f16 s, b;\n"
+      "mov.b32 {s, b}, %1;\n"
+      "add.rn.f32.f16 %0, b, %0;}\n"
+      : "+f"(acc)
+      : "r"(hdr));
+}
+
+__device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+__device__ __forceinline__ __half2 bits_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+
+// Four bytes -> two half2 of exact integers: {b0, b1}, {b2, b3}.
+__device__ __forceinline__ void bytes_to_half2(uint32_t w, uint32_t& q01, uint32_t& q23) {
+  const __half2 k1024 = bits_h2(0x64006400u);
+  q01 = h2_bits(__hsub2(bits_h2(__byte_perm(w, 0x64646464u, 0x4140)), k1024));
+  q23 = h2_bits(__hsub2(bits_h2(__byte_perm(w, 0x64646464u, 0x4342)), k1024));
+}
+
+// Eight nibbles n0..n7 (n0 = lowest 4 bits) -> four half2 of exact integers:
+// {n0, n4}, {n1, n5}, {n2, n6}, {n3, n7}.
+__device__ __forceinline__ void nibbles_to_half2(uint32_t w, uint32_t (&q)[4]) {
+  const __half2 k1024 = bits_h2(0x64006400u);
+  const __half2 k16th = bits_h2(0x2c002c00u);   // 1/16
+  const __half2 k64 = bits_h2(0x54005400u);     // 64
+  const uint32_t hi = w >> 8;
+  q[0] = h2_bits(__hsub2(bits_h2((w & 0x000f000fu) | 0x64006400u), k1024));
+  q[1] = h2_bits(__hfma2(bits_h2((w & 0x00f000f0u) | 0x64006400u), k16th, __hneg2(k64)));
+  q[2] = h2_bits(__hsub2(bits_h2((hi & 0x000f000fu) | 0x64006400u), k1024));
+  q[3] = h2_bits(__hfma2(bits_h2((hi & 0x00f000f0u) | 0x64006400u), k16th, __hneg2(k64)));
+}
+
+// One row's words into the running sums. INT8: w0 = elements e0..e0+3 -> a[0..3], w1 = the word 64
+// elements on -> a[4..7]. INT4: w0 = elements e0..e0+7 -> a[0..7] (w1 unused).
+template <bool kInt4, bool kWeighted>
+__device__ __forceinline__ void add_quantised_row(float (&a)[8], float& bias_sum, uint32_t hdr, uint32_t w0,
+                                                  uint32_t w1, float weight) {
+  if (kInt4) {
+    uint32_t q[4];
+    nibbles_to_half2(w0, q);
+    if (kWeighted) {
+      const float s = __half2float(__ushort_as_half(static_cast<unsigned short>(hdr & 0xffffu))) * weight;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = half2_bits_to_float2(q[i]);
+        a[i] = fmaf(f.x, s, a[i]);
+        a[i + 4] = fmaf(f.y, s, a[i + 4]);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        fma_code_lo(a[i], q[i], hdr);
+        fma_code_hi(a[i + 4], q[i], hdr);
+      }
+    }
+  } else {
+    uint32_t q01, q23, q45, q67;
+    bytes_to_half2(w0, q01, q23);
+    bytes_to_half2(w1, q45, q67);
+    if (kWeighted) {
+      const float s = __half2float(__ushort_as_half(static_cast<unsigned short>(hdr & 0xffffu))) * weight;
+      const float2 f0 = half2_bits_to_float2(q01), f1 = half2_bits_to_float2(q23),
+                   f2 = half2_bits_to_float2(q45), f3 = half2_bits_to_float2(q67);
+      a[0] = fmaf(f0.x, s, a[0]);
+      a[1] = fmaf(f0.y, s, a[1]);
+      a[2] = fmaf(f1.x, s, a[2]);
+      a[3] = fmaf(f1.y, s, a[3]);
+      a[4] = fmaf(f2.x, s, a[4]);
+      a[5] = fmaf(f2.y, s, a[5]);
+      a[6] = fmaf(f3.x, s, a[6]);
+      a[7] = fmaf(f3.y, s, a[7]);
+    } else {
+      fma_code_lo(a[0], q01, hdr);
+      fma_code_hi(a[1], q01, hdr);
+      fma_code_lo(a[2], q23, hdr);
+      fma_code_hi(a[3], q23, hdr);
+      fma_code_lo(a[4], q45, hdr);
+      fma_code_hi(a[5], q45, hdr);
+      fma_code_lo(a[6], q67, hdr);
+      fma_code_hi(a[7], q67, hdr);
+    }
+  }
+  if (kWeighted) {
+    bias_sum = fmaf(__half2float(__ushort_as_half(static_cast<unsigned short>(hdr >> 16))), weight, bias_sum);
+  } else {
+    add_bias(bias_sum, hdr);
+  }
+}
+
+template <typename OT, typename IndexT, bool kInt4, bool kWeighted>
+__device__ __forceinline__ void pool_quantised_bag(const NbitParams& p, const char* table, int64_t row_stride,
+                                                   int D, int64_t num_rows, int64_t col, int64_t bag, int b,
+                                                   int lane) {
+  constexpr int kSteps = kInt4 ? 4 : 2;   // rows per half-warp whose words are in flight
+  const int64_t start = load_index<IndexT>(p.offsets, bag);
+  const int64_t end = load_index<IndexT>(p.offsets, bag + 1);
+  const int len = end - start > 0x7fffffff ? 0x7fffffff : static_cast<int>(end - start);
+  const IndexT* idx = reinterpret_cast<const IndexT*>(p.indices) + start;
+  const float* psw = kWeighted ? p.per_sample_weights + start : nullptr;
+  const int half = lane >> 4, w = lane & 15;
+  // this lane's code words: INT4 word w = elements 8w..8w+7; INT8 words w and w + 16 = elements
+  // 4w..4w+3 and 64+4w..64+4w+3
+  const bool on0 = kInt4 ? 8 * w < D : 4 * w < D;
+  const bool on1 = !kInt4 && 64 + 4 * w < D;
+  const char* lane_base = table + 4 + 4 * w;
+
+  float a[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) a[e] = 0.f;
+  float bias_sum = 0.f;
+
+  for (int c = 0; c < len; c += 32) {
+    const int n = len - c < 32 ? len - c : 32;
+    uint32_t my_row = kNoRow;
+    float my_w = 1.f;
+    if (lane < n) {
+      const int64_t i = static_cast<int64_t>(__ldg(idx + c + lane));
+      if (kWeighted) my_w = __ldg(psw + c + lane);
+      if (i < 0 || i >= (num_rows >= 0 ? num_rows : int64_t{0xffffffff})) {
+        if (p.status != nullptr) atomicOr(p.status, B200TBE_DEV_INDEX_OUT_OF_RANGE);
+      } else {
+        my_row = static_cast<uint32_t>(i);
+      }
+    }
+    for (int j = 0; j < n; j += 2 * kSteps) {
+      uint32_t hdr[kSteps], w0[kSteps], w1[kSteps];
+      float wt[kSteps];
+#pragma unroll
+      for (int u = 0; u < kSteps; ++u) {
+        const int rr = j + 2 * u + half;
+        const uint32_t row = __shfl_sync(kFullMask, my_row, rr & 31);
+        wt[u] = 1.f;
+        if (kWeighted) wt[u] = __shfl_sync(kFullMask, my_w, rr & 31);
+        // a skipped row reads as scale 0, bias 0, codes 0: it adds nothing
+        hdr[u] = 0u;
+        w0[u] = 0u;
+        w1[u] = 0u;
+        if (rr < n && row != kNoRow) {
+          const char* src = lane_base + static_cast<uint64_t>(row) * static_cast<uint64_t>(row_stride);
+          hdr[u] = ldg_cached4(src - 4 - 4 * w);
+          if (on0) w0[u] = ldg_cached4(src);
+          if (on1) w1[u] = ldg_cached4(src + 64);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kSteps; ++u)
+        add_quantised_row<kInt4, kWeighted>(a, bias_sum, hdr[u], w0[u], w1[u], wt[u]);
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) a[e] += __shfl_xor_sync(kFullMask, a[e], 16);
+  bias_sum += __shfl_xor_sync(kFullMask, bias_sum, 16);
+  if (half == 0) {
+    const float scale =
+        (p.pooling_mode == B200TBE_POOL_MEAN && len > 0) ? 1.f / static_cast<float>(len) : 1.f;
+    const int rpd = static_cast<int>(p.rows_per_dest);
+    const int dest = b / rpd;
+    OT* dst = reinterpret_cast<OT* const*>(p.outputs)[dest] +
+              static_cast<int64_t>(b - dest * rpd) * p.output_stride + col;
+    float r[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) r[e] = (a[e] + bias_sum) * scale;
+    if (kInt4) {
+      // nibble order of nibbles_to_half2: a[i] = element 8w + i for i < 4 ... a[i + 4] = element 8w + 4 + i
+      if (on0) store_pooled<OT, 8>(dst + 8 * w, r);
+    } else {
+      if (on0) store_pooled<OT, 4>(dst + 4 * w, r);
+      if (on1) store_pooled<OT, 4>(dst + 64 + 4 * w, r + 4);
+    }
+  }
+}
+
+template <typename OT, typename IndexT, bool kWeighted>
+__global__ void __launch_bounds__(kNbitBagThreads, kNbitBagCtasPerSm)
+    tbe_nbit_bags_kernel(const __grid_constant__ NbitParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t bag = static_cast<int64_t>(blockIdx.x) * kNbitBagWarps + (threadIdx.x >> 5);
+  if (bag >= static_cast<int64_t>(p.T) * p.B) return;
+  const int t = static_cast<int>(bag / p.B);
+  const int b = static_cast<int>(bag - static_cast<int64_t>(t) * p.B);
+  const int ty = __ldg(p.weights_tys + t);
+  const int D_begin = __ldg(p.D_offsets + t);
+  const int D = __ldg(p.D_offsets + t + 1) - D_begin;
+  const char* table = reinterpret_cast<const char*>(p.dev_weights) + __ldg(p.weights_offsets + t);
+  const int64_t row_stride = nbit_row_stride(ty, D, p.row_alignment);
+  if (!nbit_bag_path(ty, D, table, row_stride)) return;   // the ring engine pools this table
+  const int64_t num_rows = p.rows_per_table ? __ldg(p.rows_per_table + t) : -1;
+  const int64_t col = p.output_col_offset + D_begin;
+  if (ty == B200TBE_INT4) {
+    pool_quantised_bag<OT, IndexT, true, kWeighted>(p, table, row_stride, D, num_rows, col, bag, b, lane);
+  } else {
+    pool_quantised_bag<OT, IndexT, false, kWeighted>(p, table, row_stride, D, num_rows, col, bag, b, lane);
+  }
+}
