@@ -454,7 +454,7 @@ def _bench_nbit(entry, flush, gen, iters):
     wo = torch.from_numpy(wo_np).cuda()
     Do = torch.arange(T + 1, device="cuda", dtype=torch.int32) * D
     idx, offs = torch.from_numpy(inp.indices).cuda(), torch.from_numpy(inp.offsets).cuda()
-    fn = lambda: cabi.nbit_forward(Wq, wo, tys, Do, T * D, D, idx, offs, B)
+    fn = lambda: cabi.nbit_forward(Wq, wo, tys, Do, T * D, D, idx, offs, B, table_types=(cabi.INT8, cabi.INT4))
     fn()
     ms, _ = time_launches(fn, max(5, iters // 2), flush)
     bytes_ = row_bytes + inp.num_lookups * 8 + (T * B + 1) * 8 + B * T * D * 2

@@ -141,6 +141,10 @@ typedef struct {
   int32_t index_bytes;
   int32_t pooling_mode;
   int32_t* status;
+  uint32_t table_type_mask;         /* optional: bit (1 << b200tbe_dtype) set for every type some table
+                                       has (0: unknown). Lets the call skip the kernel for the types
+                                       that are absent. A table of a type outside the mask is not
+                                       pooled. */
 } b200tbe_nbit_forward_params;
 
 B200TBE_API int b200tbe_nbit_forward(const b200tbe_nbit_forward_params* p, b200tbe_stream_t stream);

@@ -16,12 +16,16 @@ def _dev(a):
     return torch.from_numpy(np.ascontiguousarray(a)).cuda()
 
 
-def _run(W, wo, tys, Do, rows, B, indices, offsets, psw, pooling, out_dtype, row_alignment):
+def _run(W, wo, tys, Do, rows, B, indices, offsets, psw, pooling, out_dtype, row_alignment,
+         tell_types=True):
+    """tell_types: pass the set of table types along (the call may then skip the kernel of the types
+    that are absent); the result must not depend on it."""
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     out = cabi.nbit_forward(_dev(W), _dev(wo), _dev(tys), _dev(Do), int(Do[-1]),
                             int(np.max(np.diff(Do))), _dev(indices), _dev(offsets), B, pooling,
                             None if psw is None else _dev(psw), out_dtype, row_alignment,
-                            _dev(np.asarray(rows, dtype=np.int64)), status)
+                            _dev(np.asarray(rows, dtype=np.int64)), status,
+                            table_types=set(int(t) for t in tys) if tell_types else None)
     torch.cuda.synchronize()
     return out, int(status.item())
 
@@ -88,3 +92,23 @@ def test_nbit_named_config_scaled_down_against_oracle():
                        torch.float16, 16)
     assert status == 0
     np.testing.assert_allclose(got.float().cpu().numpy(), want, rtol=RTOL, atol=ATOL)
+    blind, status = _run(W, wo, tys_a, Do, [E] * T, B, inp.indices, inp.offsets, None, oracle.SUM,
+                         torch.float16, 16, tell_types=False)
+    assert status == 0 and torch.equal(blind, got)
+
+
+@pytest.mark.parametrize("ty,D", [(oracle.INT8, 128), (oracle.INT8, 4), (oracle.INT8, 68), (oracle.INT4, 128),
+                                  (oracle.INT4, 8), (oracle.INT4, 72)])
+@pytest.mark.parametrize("weighted", [False, True])
+def test_nbit_register_gather_shapes(ty, D, weighted):
+    """INT8 / INT4 rows of 4 ... 128 elements (the register-gather kernel, one or two code words per
+    lane, some lanes idle), bags of 0 ... 70 rows with ids out of range mixed in, MEAN pooling."""
+    rng = workloads.rng_for(310 + D)
+    rows, B = [500, 37], 97
+    W, wo, Do, tys_a = helpers.quantised_tables(rng, rows, [D, D], [ty, ty], 16)
+    _, offsets, indices = helpers.ragged_bags(rng, 2, B, rows, 0, 70, empty_fraction=0.1)
+    psw = rng.random(indices.size).astype(np.float32) if weighted else None
+    want = oracle.nbit_forward(W, wo, tys_a, Do, 16, B, indices, offsets, psw, oracle.MEAN)
+    got, status = _run(W, wo, tys_a, Do, rows, B, indices, offsets, psw, oracle.MEAN, torch.float32, 16)
+    assert status == 0
+    np.testing.assert_allclose(got.cpu().numpy(), want, rtol=1e-5, atol=1e-5)

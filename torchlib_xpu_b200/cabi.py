@@ -47,7 +47,7 @@ class NbitForwardParams(ctypes.Structure):
         ("num_dests", ctypes.c_int32), ("T", ctypes.c_int32), ("B", ctypes.c_int32),
         ("max_D", ctypes.c_int32), ("row_alignment", ctypes.c_int32),
         ("output_dtype", ctypes.c_int32), ("index_bytes", ctypes.c_int32),
-        ("pooling_mode", ctypes.c_int32), ("status", _c_void_p),
+        ("pooling_mode", ctypes.c_int32), ("status", _c_void_p), ("table_type_mask", ctypes.c_uint32),
     ]
 
 
@@ -222,7 +222,10 @@ def forward(dev_weights, weights_offsets, D_offsets, total_D, max_D, indices, of
 
 def nbit_forward(dev_weights, weights_offsets, weights_tys, D_offsets, total_D, max_D, indices,
                  offsets, B, pooling_mode=POOL_SUM, per_sample_weights=None,
-                 output_dtype=torch.float16, row_alignment=16, rows_per_table=None, status=None):
+                 output_dtype=torch.float16, row_alignment=16, rows_per_table=None, status=None,
+                 table_types=None):
+    """b200tbe_nbit_forward over torch tensors. table_types: the type codes present among the tables
+    (any iterable of ints), when the caller knows them on the host; None: unknown."""
     T = weights_offsets.numel()
     p = NbitForwardParams()
     p.dev_weights, p.weights_offsets, p.weights_tys = _p(dev_weights), _p(weights_offsets), _p(weights_tys)
@@ -237,6 +240,9 @@ def nbit_forward(dev_weights, weights_offsets, weights_tys, D_offsets, total_D, 
     p.index_bytes = _index_bytes(indices, offsets)
     p.pooling_mode = pooling_mode
     p.status = _p(status)
+    p.table_type_mask = 0
+    for code in (table_types or ()):
+        p.table_type_mask |= 1 << int(code)
     check(lib().b200tbe_nbit_forward(ctypes.byref(p), _stream()), "b200tbe_nbit_forward")
     return out
 

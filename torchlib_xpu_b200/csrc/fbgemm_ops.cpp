@@ -613,6 +613,10 @@ Tensor int_nbit_split_embedding_codegen_lookup_function(
   p.max_D = static_cast<int32_t>(std::max({max_int2_D, max_int4_D, max_int8_D, max_float16_D,
                                            max_float32_D}));
   p.row_alignment = static_cast<int32_t>(row_alignment.value_or(16));
+  // the per-type maxima say which types exist at all
+  p.table_type_mask = (max_int2_D > 0 ? 1u << B200TBE_INT2 : 0u) | (max_int4_D > 0 ? 1u << B200TBE_INT4 : 0u) |
+                      (max_int8_D > 0 ? 1u << B200TBE_INT8 : 0u) | (max_float16_D > 0 ? 1u << B200TBE_FP16 : 0u) |
+                      (max_float32_D > 0 ? 1u << B200TBE_FP32 : 0u);
   // Row counts for the range check: the op's argument list does not carry them, but a table ends no
   // later than where the nearest following table begins (or dev_weights ends), so
   // rows_t <= bytes_t / stride_t: an id beyond that would read another table's bytes.

@@ -1,6 +1,11 @@
 // Quantised-inference TBE forward: INT8 / INT4 / INT2 row-wise quantised tables with an fp16
-// {scale, bias} header per row, plus FP16 / FP32 tables, mixed per table, on the streaming gather
-// engine of tbe_stream.cuh.
+// {scale, bias} header per row, plus FP16 / FP32 tables, mixed per table.
+//
+// Two kernels share a call. INT8 and INT4 tables of at most 128 elements per row -- what inference
+// tables are -- go through the register gather of tbe_nbit_bags.cuh (one warp per bag, code words
+// fetched straight into registers). Everything else (INT2, float rows, wider rows, rows that are
+// not 4-byte aligned) goes through the streaming gather engine of tbe_stream.cuh, described next;
+// each kernel skips the other's tables.
 //
 // A whole row (header + payload, rounded up to 16 bytes) is brought to shared memory. The consuming
 // warp reads it one row per instruction: every lane loads the 4-byte header (a shared-memory
@@ -9,11 +14,7 @@
 // in global memory. q * (scale * weight) is accumulated per element in fp32 and bias * weight once
 // per row; the bias sum is added when the bag is written.
 //
-// Measured alternative, not kept: one warp per bag with the row pieces gathered straight into
-// registers (the shape that wins for float rows, tbe_bags.cuh) took 2.8 ms on the 64-table INT8/INT4
-// configuration against 2.2 ms here: with the header in the first piece only 9 of 16 lanes of a
-// group carry payload, and the dequantisation arithmetic, not the gather, is what bounds this op.
-#include "tbe_stream.cuh"
+#include "tbe_bags.cuh"
 
 namespace b200tbe {
 namespace {
@@ -39,9 +40,32 @@ struct NbitParams {
   int32_t bags_per_unit;
   int32_t units_per_table;
   int64_t num_units;
+  int32_t only_bag_tables;   // the caller vouches that every table is INT8 / INT4: no ring kernel
 };
 
 __device__ __forceinline__ int64_t round_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
+
+// Bytes of a row's header and payload, and the distance between rows.
+__device__ __forceinline__ void nbit_row_geometry(int ty, int D, int row_alignment, int& header,
+                                                  int64_t& payload, int64_t& row_stride) {
+  header = 4;
+  switch (ty) {
+    case B200TBE_INT8: payload = D; break;
+    case B200TBE_INT4: payload = (D + 1) / 2; break;
+    case B200TBE_INT2: payload = (D + 3) / 4; break;
+    case B200TBE_FP16: payload = int64_t{D} * 2; header = 0; break;
+    default: payload = int64_t{D} * 4; header = 0; break;
+  }
+  row_stride = round_up(header + payload, row_alignment);
+}
+__device__ __forceinline__ int64_t nbit_row_stride(int ty, int D, int row_alignment) {
+  int header;
+  int64_t payload, stride;
+  nbit_row_geometry(ty, D, row_alignment, header, payload, stride);
+  return stride;
+}
+
+#include "tbe_nbit_bags.cuh"
 
 template <typename OT, typename IndexT, int kVPL>
 __global__ void __launch_bounds__(kStreamThreads, 1)
@@ -68,16 +92,10 @@ __global__ void __launch_bounds__(kStreamThreads, 1)
     const int64_t col = p.output_col_offset + D_begin;
     OT* const* outputs = reinterpret_cast<OT* const*>(p.outputs);
 
-    int64_t payload;
-    int header = 4;
-    switch (ty) {
-      case B200TBE_INT8: payload = D; break;
-      case B200TBE_INT4: payload = (D + 1) / 2; break;
-      case B200TBE_INT2: payload = (D + 3) / 4; break;
-      case B200TBE_FP16: payload = int64_t{D} * 2; header = 0; break;
-      default: payload = int64_t{D} * 4; header = 0; break;
-    }
-    const int64_t row_stride = round_up(header + payload, p.row_alignment);
+    int64_t payload, row_stride;
+    int header;
+    nbit_row_geometry(ty, D, p.row_alignment, header, payload, row_stride);
+    if (nbit_bag_path(ty, D, table, row_stride)) continue;   // pooled by tbe_nbit_bags_kernel
     const int64_t copy_bytes = round_up(header + payload, 16);
     const bool streamable = (D & 3) == 0 && D > 0 && (row_stride & 15) == 0 &&
                             (reinterpret_cast<uintptr_t>(table) & 15) == 0 &&
@@ -126,7 +144,22 @@ int launch_one(const NbitParams& d, cudaStream_t stream) {
 }
 
 template <typename OT, typename IndexT>
+int launch_bags(const NbitParams& d, cudaStream_t stream) {
+  const int64_t bags = static_cast<int64_t>(d.T) * d.B;
+  const int64_t ctas = (bags + kNbitBagWarps - 1) / kNbitBagWarps;
+  if (ctas > 0x7fffffff) return B200TBE_ERR_TOO_LARGE;
+  if (d.per_sample_weights != nullptr) {
+    tbe_nbit_bags_kernel<OT, IndexT, true><<<static_cast<unsigned>(ctas), kNbitBagThreads, 0, stream>>>(d);
+  } else {
+    tbe_nbit_bags_kernel<OT, IndexT, false><<<static_cast<unsigned>(ctas), kNbitBagThreads, 0, stream>>>(d);
+  }
+  return launch_status();
+}
+
+template <typename OT, typename IndexT>
 int launch_nbit(const NbitParams& d, int max_D, cudaStream_t stream) {
+  const int st = launch_bags<OT, IndexT>(d, stream);
+  if (st != B200TBE_OK || d.only_bag_tables) return st;
   if (max_D <= 128) return launch_one<OT, IndexT, 1>(d, stream);
   if (max_D <= 256) return launch_one<OT, IndexT, 2>(d, stream);
   if (max_D <= 512) return launch_one<OT, IndexT, 4>(d, stream);
@@ -177,6 +210,11 @@ extern "C" int b200tbe_nbit_forward(const b200tbe_nbit_forward_params* p,
   d.bags_per_unit = stream_bags_per_unit(p->T, p->B);
   d.units_per_table = (p->B + d.bags_per_unit - 1) / d.bags_per_unit;
   d.num_units = static_cast<int64_t>(p->T) * d.units_per_table;
+  // types present, when the caller says (bit i: some table has type code i): with INT8 and INT4
+  // alone and narrow rows the ring kernel would find nothing to do and is not launched
+  const uint32_t fast_types = (1u << B200TBE_INT8) | (1u << B200TBE_INT4);
+  d.only_bag_tables = p->table_type_mask != 0 && (p->table_type_mask & ~fast_types) == 0 &&
+                      p->max_D <= kNbitBagMaxD && p->row_alignment % 4 == 0;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   const bool i64 = p->index_bytes == 8;
   if (p->output_dtype == B200TBE_FP32)

@@ -21,13 +21,14 @@
 
 constexpr int kNbitBagWarps = 8;
 constexpr int kNbitBagThreads = kNbitBagWarps * 32;
-constexpr int kNbitBagCtasPerSm = 6;
+constexpr int kNbitBagCtasPerSm = 6;   // 48 warps per SM at 40 registers (a few spilled words); 5 CTAs measured 6 % slower
 constexpr int kNbitBagMaxD = 128;
 
 // Tables this kernel takes; everything else (INT2, float rows, wider or oddly aligned rows) stays
 // on the ring engine. Both kernels evaluate this, so every table is pooled exactly once.
 __device__ __forceinline__ bool nbit_bag_path(int ty, int D, const char* table, int64_t row_stride) {
-  if (D <= 0 || D > kNbitBagMaxD || (row_stride & 3) != 0 || (reinterpret_cast<uintptr_t>(table) & 3) != 0)
+  if (D <= 0 || D > kNbitBagMaxD || (row_stride & 3) != 0 || row_stride > 4096 ||
+      (reinterpret_cast<uintptr_t>(table) & 3) != 0)
     return false;
   if (ty == B200TBE_INT8) return (D & 3) == 0;
   if (ty == B200TBE_INT4) return (D & 7) == 0;
@@ -40,30 +41,29 @@ __device__ __forceinline__ uint32_t ldg_cached4(const void* p) {
   return v;
 }
 
-// acc += code (fp16, low or high half of q2) * scale (fp16, low half of hdr), fp32 accumulate.
-__device__ __forceinline__ void fma_code_lo(float& acc, uint32_t q2, uint32_t hdr) {
-  asm("{.reg .f16 ql, qh, s, b;\n"
-      "mov.b32 {ql, qh}, %1;\n"
-      "mov.b32 {s, b}, %2;\n"
-      "fma.rn.f32.f16 %0, ql, s, %0;}\n"
-      : "+f"(acc)
-      : "r"(q2), "r"(hdr));
-}
-__device__ __forceinline__ void fma_code_hi(float& acc, uint32_t q2, uint32_t hdr) {
-  asm("{.reg .f16 ql, qh, s, b;\n"
-      "mov.b32 {ql, qh}, %1;\n"
-      "mov.b32 {s, b}, %2;\n"
-      "fma.rn.f32.f16 %0, qh, s, %0;}\n"
-      : "+f"(acc)
-      : "r"(q2), "r"(hdr));
-}
-// acc += bias (fp16, high half of hdr)
-__device__ __forceinline__ void add_bias(float& acc, uint32_t hdr) {
-  asm("{.reg .f16 s, b;\n"
-      "mov.b32 {s, b}, %1;\n"
-      "add.rn.f32.f16 %0, b, %0;}\n"
-      : "+f"(acc)
-      : "r"(hdr));
+// a[i] += code i * scale for the eight codes held as four half2 {q0: codes 0,1; q1: 2,3; q2: 4,5;
+// q3: 6,7} (exact fp16 integers), scale = low half of hdr; bias_sum += bias = high half of hdr. One
+// block, so every register pair is split into its halves once.
+__device__ __forceinline__ void fma_codes8(float (&a)[8], float& bias_sum, uint32_t q0, uint32_t q1,
+                                           uint32_t q2, uint32_t q3, uint32_t hdr) {
+  asm("{.reg .f16 s, b, x0, x1, x2, x3, x4, x5, x6, x7;\n"
+      "mov.b32 {s, b}, %9;\n"
+      "mov.b32 {x0, x1}, %10;\n"
+      "mov.b32 {x2, x3}, %11;\n"
+      "mov.b32 {x4, x5}, %12;\n"
+      "mov.b32 {x6, x7}, %13;\n"
+      "fma.rn.f32.f16 %0, x0, s, %0;\n"
+      "fma.rn.f32.f16 %1, x1, s, %1;\n"
+      "fma.rn.f32.f16 %2, x2, s, %2;\n"
+      "fma.rn.f32.f16 %3, x3, s, %3;\n"
+      "fma.rn.f32.f16 %4, x4, s, %4;\n"
+      "fma.rn.f32.f16 %5, x5, s, %5;\n"
+      "fma.rn.f32.f16 %6, x6, s, %6;\n"
+      "fma.rn.f32.f16 %7, x7, s, %7;\n"
+      "add.rn.f32.f16 %8, b, %8;}\n"
+      : "+f"(a[0]), "+f"(a[1]), "+f"(a[2]), "+f"(a[3]), "+f"(a[4]), "+f"(a[5]), "+f"(a[6]), "+f"(a[7]),
+        "+f"(bias_sum)
+      : "r"(hdr), "r"(q0), "r"(q1), "r"(q2), "r"(q3));
 }
 
 __device__ __forceinline__ uint32_t h2_bits(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
@@ -90,7 +90,7 @@ __device__ __forceinline__ void nibbles_to_half2(uint32_t w, uint32_t (&q)[4]) {
 }
 
 // One row's words into the running sums. INT8: w0 = elements e0..e0+3 -> a[0..3], w1 = the word 64
-// elements on -> a[4..7]. INT4: w0 = elements e0..e0+7 -> a[0..7] (w1 unused).
+// elements on -> a[4..7]. INT4: w0 = nibbles n0..n7 -> a[2i] += n_i, a[2i + 1] += n_(i+4) (w1 unused).
 template <bool kInt4, bool kWeighted>
 __device__ __forceinline__ void add_quantised_row(float (&a)[8], float& bias_sum, uint32_t hdr, uint32_t w0,
                                                   uint32_t w1, float weight) {
@@ -102,15 +102,11 @@ __device__ __forceinline__ void add_quantised_row(float (&a)[8], float& bias_sum
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const float2 f = half2_bits_to_float2(q[i]);
-        a[i] = fmaf(f.x, s, a[i]);
-        a[i + 4] = fmaf(f.y, s, a[i + 4]);
+        a[2 * i] = fmaf(f.x, s, a[2 * i]);
+        a[2 * i + 1] = fmaf(f.y, s, a[2 * i + 1]);
       }
     } else {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        fma_code_lo(a[i], q[i], hdr);
-        fma_code_hi(a[i + 4], q[i], hdr);
-      }
+      fma_codes8(a, bias_sum, q[0], q[1], q[2], q[3], hdr);
     }
   } else {
     uint32_t q01, q23, q45, q67;
@@ -129,38 +125,31 @@ __device__ __forceinline__ void add_quantised_row(float (&a)[8], float& bias_sum
       a[6] = fmaf(f3.x, s, a[6]);
       a[7] = fmaf(f3.y, s, a[7]);
     } else {
-      fma_code_lo(a[0], q01, hdr);
-      fma_code_hi(a[1], q01, hdr);
-      fma_code_lo(a[2], q23, hdr);
-      fma_code_hi(a[3], q23, hdr);
-      fma_code_lo(a[4], q45, hdr);
-      fma_code_hi(a[5], q45, hdr);
-      fma_code_lo(a[6], q67, hdr);
-      fma_code_hi(a[7], q67, hdr);
+      fma_codes8(a, bias_sum, q01, q23, q45, q67, hdr);
     }
   }
-  if (kWeighted) {
+  if (kWeighted)
     bias_sum = fmaf(__half2float(__ushort_as_half(static_cast<unsigned short>(hdr >> 16))), weight, bias_sum);
-  } else {
-    add_bias(bias_sum, hdr);
-  }
 }
 
-template <typename OT, typename IndexT, bool kInt4, bool kWeighted>
-__device__ __forceinline__ void pool_quantised_bag(const NbitParams& p, const char* table, int64_t row_stride,
+// kFull: D = 128, every lane of a half-warp has its code words (no lane sits out).
+template <typename OT, typename IndexT, bool kInt4, bool kWeighted, bool kFull>
+__device__ __forceinline__ void pool_quantised_bag(const NbitParams& p, const char* table, uint32_t row_stride,
                                                    int D, int64_t num_rows, int64_t col, int64_t bag, int b,
                                                    int lane) {
   constexpr int kSteps = kInt4 ? 4 : 2;   // rows per half-warp whose words are in flight
   const int64_t start = load_index<IndexT>(p.offsets, bag);
   const int64_t end = load_index<IndexT>(p.offsets, bag + 1);
-  const int len = end - start > 0x7fffffff ? 0x7fffffff : static_cast<int>(end - start);
+  int len = end - start > 0x7fffffff ? 0x7fffffff : static_cast<int>(end - start);
+  const int pooled = len;                 // MEAN divides by the bag's length, skipped ids included
+  if (num_rows == 0) len = 0;             // a table without rows: every id is out of range
   const IndexT* idx = reinterpret_cast<const IndexT*>(p.indices) + start;
   const float* psw = kWeighted ? p.per_sample_weights + start : nullptr;
   const int half = lane >> 4, w = lane & 15;
   // this lane's code words: INT4 word w = elements 8w..8w+7; INT8 words w and w + 16 = elements
   // 4w..4w+3 and 64+4w..64+4w+3
-  const bool on0 = kInt4 ? 8 * w < D : 4 * w < D;
-  const bool on1 = !kInt4 && 64 + 4 * w < D;
+  const bool on0 = kFull || (kInt4 ? 8 * w < D : 4 * w < D);
+  const bool on1 = !kInt4 && (kFull || 64 + 4 * w < D);
   const char* lane_base = table + 4 + 4 * w;
 
   float a[8];
@@ -170,7 +159,10 @@ __device__ __forceinline__ void pool_quantised_bag(const NbitParams& p, const ch
 
   for (int c = 0; c < len; c += 32) {
     const int n = len - c < 32 ? len - c : 32;
-    uint32_t my_row = kNoRow;
+    // this lane's row id; a skipped lookup (past the bag's end, id out of range) reads row 0 with
+    // its header replaced by zero: scale 0 and bias 0 add nothing, and no load needs a test
+    uint32_t my_row = 0;
+    bool my_ok = false;
     float my_w = 1.f;
     if (lane < n) {
       const int64_t i = static_cast<int64_t>(__ldg(idx + c + lane));
@@ -179,27 +171,26 @@ __device__ __forceinline__ void pool_quantised_bag(const NbitParams& p, const ch
         if (p.status != nullptr) atomicOr(p.status, B200TBE_DEV_INDEX_OUT_OF_RANGE);
       } else {
         my_row = static_cast<uint32_t>(i);
+        my_ok = true;
       }
     }
+    const uint32_t ok_mask = __ballot_sync(kFullMask, my_ok);
     for (int j = 0; j < n; j += 2 * kSteps) {
       uint32_t hdr[kSteps], w0[kSteps], w1[kSteps];
       float wt[kSteps];
 #pragma unroll
       for (int u = 0; u < kSteps; ++u) {
-        const int rr = j + 2 * u + half;
-        const uint32_t row = __shfl_sync(kFullMask, my_row, rr & 31);
+        const int rr = (j + 2 * u + half) & 31;
+        const uint32_t row = __shfl_sync(kFullMask, my_row, rr);
         wt[u] = 1.f;
-        if (kWeighted) wt[u] = __shfl_sync(kFullMask, my_w, rr & 31);
-        // a skipped row reads as scale 0, bias 0, codes 0: it adds nothing
-        hdr[u] = 0u;
+        if (kWeighted) wt[u] = __shfl_sync(kFullMask, my_w, rr);
+        const char* src = lane_base + static_cast<uint64_t>(row) * row_stride;
+        hdr[u] = ldg_cached4(src - 4 - 4 * w);
         w0[u] = 0u;
         w1[u] = 0u;
-        if (rr < n && row != kNoRow) {
-          const char* src = lane_base + static_cast<uint64_t>(row) * static_cast<uint64_t>(row_stride);
-          hdr[u] = ldg_cached4(src - 4 - 4 * w);
-          if (on0) w0[u] = ldg_cached4(src);
-          if (on1) w1[u] = ldg_cached4(src + 64);
-        }
+        if (on0) w0[u] = ldg_cached4(src);
+        if (on1) w1[u] = ldg_cached4(src + 64);
+        if (((ok_mask >> rr) & 1u) == 0 || j + 2 * u + half >= 32) hdr[u] = 0u;
       }
 #pragma unroll
       for (int u = 0; u < kSteps; ++u)
@@ -211,7 +202,7 @@ __device__ __forceinline__ void pool_quantised_bag(const NbitParams& p, const ch
   bias_sum += __shfl_xor_sync(kFullMask, bias_sum, 16);
   if (half == 0) {
     const float scale =
-        (p.pooling_mode == B200TBE_POOL_MEAN && len > 0) ? 1.f / static_cast<float>(len) : 1.f;
+        (p.pooling_mode == B200TBE_POOL_MEAN && pooled > 0) ? 1.f / static_cast<float>(pooled) : 1.f;
     const int rpd = static_cast<int>(p.rows_per_dest);
     const int dest = b / rpd;
     OT* dst = reinterpret_cast<OT* const*>(p.outputs)[dest] +
@@ -220,8 +211,9 @@ __device__ __forceinline__ void pool_quantised_bag(const NbitParams& p, const ch
 #pragma unroll
     for (int e = 0; e < 8; ++e) r[e] = (a[e] + bias_sum) * scale;
     if (kInt4) {
-      // nibble order of nibbles_to_half2: a[i] = element 8w + i for i < 4 ... a[i + 4] = element 8w + 4 + i
-      if (on0) store_pooled<OT, 8>(dst + 8 * w, r);
+      // nibbles_to_half2 pairs nibble i with nibble i + 4: a[2i] = element 8w + i, a[2i + 1] = element 8w + 4 + i
+      const float e[8] = {r[0], r[2], r[4], r[6], r[1], r[3], r[5], r[7]};
+      if (on0) store_pooled<OT, 8>(dst + 8 * w, e);
     } else {
       if (on0) store_pooled<OT, 4>(dst + 4 * w, r);
       if (on1) store_pooled<OT, 4>(dst + 64 + 4 * w, r + 4);
@@ -245,9 +237,18 @@ __global__ void __launch_bounds__(kNbitBagThreads, kNbitBagCtasPerSm)
   if (!nbit_bag_path(ty, D, table, row_stride)) return;   // the ring engine pools this table
   const int64_t num_rows = p.rows_per_table ? __ldg(p.rows_per_table + t) : -1;
   const int64_t col = p.output_col_offset + D_begin;
+  const uint32_t stride = static_cast<uint32_t>(row_stride);   // at most 4 + 128 bytes plus padding
   if (ty == B200TBE_INT4) {
-    pool_quantised_bag<OT, IndexT, true, kWeighted>(p, table, row_stride, D, num_rows, col, bag, b, lane);
+    if (D == kNbitBagMaxD) {
+      pool_quantised_bag<OT, IndexT, true, kWeighted, true>(p, table, stride, D, num_rows, col, bag, b, lane);
+    } else {
+      pool_quantised_bag<OT, IndexT, true, kWeighted, false>(p, table, stride, D, num_rows, col, bag, b, lane);
+    }
   } else {
-    pool_quantised_bag<OT, IndexT, false, kWeighted>(p, table, row_stride, D, num_rows, col, bag, b, lane);
+    if (D == kNbitBagMaxD) {
+      pool_quantised_bag<OT, IndexT, false, kWeighted, true>(p, table, stride, D, num_rows, col, bag, b, lane);
+    } else {
+      pool_quantised_bag<OT, IndexT, false, kWeighted, false>(p, table, stride, D, num_rows, col, bag, b, lane);
+    }
   }
 }
