@@ -624,19 +624,34 @@ __global__ void __launch_bounds__(kSweepThreads)
     on[c] = (c * GS + gl) * 4 < D;
     acc[c] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  // piece 0 = tail slot of `span`; piece i >= 1 = head slot of span + i
+  // piece 0 = tail slot of `span`; piece i >= 1 = head slot of span + i. A row looked up 150 000
+  // times leaves almost 600 pieces to one warp, so eight pieces are requested before the first is
+  // added (the additions keep their order).
+  constexpr int kPieces = 8 / kC;
   const float* lane_base = p.partials + (gl * 4);
-  for (uint32_t i = grp; i <= heads; i += NG) {
-    const int64_t slot = i == 0 ? 2 * static_cast<int64_t>(span) + 1 : 2 * static_cast<int64_t>(span + i);
-    const float* src = lane_base + slot * p.max_D;
+  auto slot_of = [&](uint32_t i) -> int64_t {
+    return i == 0 ? 2 * static_cast<int64_t>(span) + 1 : 2 * static_cast<int64_t>(span + i);
+  };
+  for (uint32_t i0 = grp; i0 <= heads; i0 += NG * kPieces) {
+    float4 x[kPieces][kC];
 #pragma unroll
-    for (int c = 0; c < kC; ++c) {
-      if (on[c]) {
-        const float4 x = *reinterpret_cast<const float4*>(src + c * GS * 4);
-        acc[c].x += x.x;
-        acc[c].y += x.y;
-        acc[c].z += x.z;
-        acc[c].w += x.w;
+    for (int u = 0; u < kPieces; ++u) {
+      const uint32_t i = i0 + u * NG;
+      const float* src = lane_base + slot_of(i <= heads ? i : i0) * p.max_D;
+#pragma unroll
+      for (int c = 0; c < kC; ++c) {
+        x[u][c] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (i <= heads && on[c]) x[u][c] = *reinterpret_cast<const float4*>(src + c * GS * 4);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kPieces; ++u) {
+#pragma unroll
+      for (int c = 0; c < kC; ++c) {
+        acc[c].x += x[u][c].x;
+        acc[c].y += x[u][c].y;
+        acc[c].z += x[u][c].z;
+        acc[c].w += x[u][c].w;
       }
     }
   }

@@ -114,6 +114,9 @@ __device__ __forceinline__ void pool_float_bag(const BagLaunch<OT>& p, const cha
   const int v = lane & (gs - 1);         // this lane's vector inside the row
   const bool active = v < vecs;
   const char* lane_base = table + (v << 4);
+  // lanes beyond the row's last vector (rows that are not a power of two of vectors) re-read the
+  // last one in the test-free rounds; their sums are never stored
+  const char* lane_any = table + ((active ? v : vecs - 1) << 4);
 
   float acc[kE];
 #pragma unroll
@@ -133,7 +136,32 @@ __device__ __forceinline__ void pool_float_bag(const BagLaunch<OT>& p, const cha
         my_row = static_cast<uint32_t>(i);
       }
     }
-    for (int j = 0; j < n; j += G * kLoads) {
+    // rounds of G * kLoads rows. A round whose rows all exist and are in range -- every round but a
+    // bag's last, unless an id is bad -- loads without a test
+    const uint32_t bad = __ballot_sync(kFullMask, my_row == kNoRow);   // lanes >= n included
+    const int n_clean = bad == 0 ? 32 : __ffs(bad) - 1;                // rows [0, n_clean) are all good
+    const int round_rows = G * kLoads;
+    int j = 0;
+    for (; j + round_rows <= n_clean; j += round_rows) {
+      uint4 x[kLoads];
+      float w[kLoads];
+#pragma unroll
+      for (int u = 0; u < kLoads; ++u) {
+        const int rr = j + u * G + h;
+        const uint32_t row = __shfl_sync(kFullMask, my_row, rr);
+        if (kWeighted) w[u] = __shfl_sync(kFullMask, my_w, rr);
+        x[u] = ldg_cached16(lane_any + static_cast<uint64_t>(row) * static_cast<uint32_t>(row_bytes));
+      }
+#pragma unroll
+      for (int u = 0; u < kLoads; ++u) {
+        if (kWeighted) {
+          Vec16<WT>::fma(acc, x[u], w[u]);
+        } else {
+          Vec16<WT>::add(acc, x[u]);
+        }
+      }
+    }
+    for (; j < n; j += G * kLoads) {
       uint4 x[kLoads];
       float w[kLoads];
 #pragma unroll
