@@ -33,9 +33,10 @@ L2_FLUSH_BYTES = 512 << 20
 # rows x D=128, B=65536, about 1.67 M lookups -- from the ncu capture summarised in
 # profiles/tbe_step_one_table_traffic.md. Tables are processed one after another, each with its own
 # rows, ids and gradient columns, so a step of T tables moves T times this.
-FWD_TRAFFIC_PER_TABLE = None
-BWD_TRAFFIC_PER_TABLE = None
-TRAFFIC_NOTE = ("one-table ncu capture x tables (profiles/tbe_step_one_table_traffic.md)")
+FWD_TRAFFIC_PER_TABLE = 109.9e6   # lookup kernel: 103.1 MB read + 6.8 MB written
+BWD_TRAFFIC_PER_TABLE = 256.2e6   # 20 kernels of one b200tbe_backward call: 213.4 MB read + 42.8 MB written
+TRAFFIC_NOTE = ("one-table ncu capture x tables (profiles/tbe_step_one_table_traffic.md); bytes a kernel leaves "
+                "dirty in L2 when it ends are not in its DRAM write counter")
 TABLES_OVERRIDE = None   # --tables: fewer tables for --only runs (small profiler captures)
 
 
@@ -642,8 +643,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-others", action="store_true", help="skip the single-kernel configurations")
     ap.add_argument("--small", action="store_true", help="tiny tables, for profiler captures and smoke runs")
-    ap.add_argument("--only", default=None, choices=["jagged", "fp32", "train", "nbit", "nv12", "permute"],
-                    help="run one single-GPU configuration alone (few launches; for profiler captures)")
+    ap.add_argument("--only", default=None, choices=["jagged", "fp32", "train", "nbit", "nv12", "permute", "step"],
+                    help="run one single-GPU configuration alone (few launches; for profiler captures); "
+                         "'step' is the bench step itself cut to --tables tables (default 2)")
     ap.add_argument("--iters", type=int, default=20, help="timed launches per single-GPU configuration")
     ap.add_argument("--tables", type=int, default=None,
                     help="with --only train|nbit: use this many tables (a small case for profiler captures)")
@@ -669,6 +671,16 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     cabi.lib()
     peak_gbs, peak_kind = measured_peak_gbs()
+    if args.only == "step":
+        # the bench step on a few tables: --iters backwards, then --iters forwards (same kernels, same
+        # per-table sizes as the full step; small enough for full-metric profiler captures)
+        small_cfg = dict(cfg, T_per_gpu=args.tables or 2)
+        st = ShardedTbeStep(0, 1, small_cfg)
+        bwd_ms, _ = time_launches(st.backward, args.iters)
+        fwd_ms, _ = time_launches(st.forward, args.iters)
+        print(json.dumps({"only": "step", "tables": st.T, "lookups": st.N, "unique_rows": st.U,
+                          "backward_ms": bwd_ms, "forward_ms": fwd_ms}), file=json_out, flush=True)
+        return
     if args.only is not None:
         global TABLES_OVERRIDE
         TABLES_OVERRIDE = args.tables
