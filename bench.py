@@ -130,8 +130,8 @@ def uniform_half_table(num_elems, lo, hi, gen):
 
 def backward_launches(row_bits: int) -> int:
     """Kernels one b200tbe_backward call launches for rows of at most 512 elements: two plan kernels,
-    linearize, per sort pass (11 bits each) histogram + 3 scan kernels + scatter, sweep, finish."""
-    passes = (row_bits + 10) // 11
+    linearize, per sort pass (8 bits each) histogram + 3 scan kernels + scatter, sweep, finish."""
+    passes = (row_bits + 7) // 8
     return 2 + 1 + passes * 5 + 2
 
 

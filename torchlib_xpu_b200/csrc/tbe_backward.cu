@@ -892,11 +892,11 @@ int launch_sweep(const BwdDev& d, int max_tiles, cudaStream_t stream) {
   constexpr int kSpansPerCta = kSweepWarps * (32 / GS);
   const int64_t ctas = static_cast<int64_t>(max_tiles) * (kSpansPerTile / kSpansPerCta);
   const int64_t spans = static_cast<int64_t>(max_tiles) * kSpansPerTile;
-  if (ctas > 0x7fffffff || spans / kSweepWarps > 0x7fffffff) return B200TBE_ERR_TOO_LARGE;
+  if (ctas > 0x7fffffff || spans / kFinishWarps > 0x7fffffff) return B200TBE_ERR_TOO_LARGE;
   sweep_runs_kernel<WT, GT, kScaled, GS, kC, sweep_ctas_per_sm<WT, GT, kC>()>
       <<<static_cast<unsigned>(ctas), kSweepThreads, 0, stream>>>(d);
   finish_open_runs_kernel<WT, GS, kC>
-      <<<static_cast<unsigned>(spans / kSweepWarps), kSweepThreads, 0, stream>>>(d);
+      <<<static_cast<unsigned>(spans / kFinishWarps), kFinishWarps * 32, 0, stream>>>(d);
   return launch_status();
 }
 

@@ -29,8 +29,13 @@
 
 constexpr int kSpan = 256;                                  // sorted positions per span
 constexpr int kSpansPerTile = kSortPlanTile / kSpan;        // 16
-constexpr int kSweepWarps = 4;
+// One warp per CTA: spans finish at very different times (a span inside a long run is pure
+// streaming, a span of one-lookup runs updates a row every other position), and a CTA keeps its
+// slot until its slowest warp is done. Measured on the bench step: 4 warps per CTA 9.65 ms for the
+// backward, 2 warps 9.67, 1 warp 8.85 at the same registers, 7.99 with 32 such CTAs per SM.
+constexpr int kSweepWarps = 1;
 constexpr int kSweepThreads = kSweepWarps * 32;
+constexpr int kFinishWarps = 4;
 // positions whose gradient slices are in flight per group (fewer when a lane holds more of a row)
 template <int kC>
 __host__ __device__ constexpr int sweep_loads() {
@@ -44,7 +49,9 @@ __host__ __device__ constexpr int sweep_loads_for() {
 }
 template <typename WT, typename GT, int kC>
 __host__ __device__ constexpr int sweep_ctas_per_sm() {
-  return kC > 2 ? 4 : (kC == 2 ? (sizeof(WT) == 2 && sizeof(GT) == 2 ? 5 : 4) : 6);
+  // CTAs (= warps) per SM; the register file allows 65536 / (32 * this) registers per thread
+  return kC > 2 ? 16 : (kC == 2 ? (sizeof(WT) == 2 && sizeof(GT) == 2 ? 20 : 16)
+                                : (sizeof(WT) == 2 && sizeof(GT) == 2 ? 32 : 24));
 }
 constexpr uint32_t kNoSlice = 0xffffffffu;
 constexpr uint32_t kSpanTailOwner = 1u;   // the span's last run continues to the right; its piece is in the tail slot
@@ -583,13 +590,13 @@ __global__ void __launch_bounds__(kSweepThreads, kMinCtas)
 // the span's tail slot, then the head slot of every following span up to and including the first
 // one that the run does not pass through -- and updates the row. Group g takes pieces g, g + NG, ...
 template <typename WT, int GS, int kC>
-__global__ void __launch_bounds__(kSweepThreads)
+__global__ void __launch_bounds__(kFinishWarps * 32)
     finish_open_runs_kernel(const __grid_constant__ BwdDev p) {
   constexpr int NG = 32 / GS;
   constexpr int quad_w = GS * 4 * static_cast<int>(sizeof(WT));
   const int lane = threadIdx.x & 31;
   const int grp = lane / GS, gl = lane % GS;
-  const uint32_t span = blockIdx.x * kSweepWarps + (threadIdx.x >> 5);
+  const uint32_t span = blockIdx.x * kFinishWarps + (threadIdx.x >> 5);
   const uint32_t tile = span / kSpansPerTile;
   const uint32_t live_tiles = __ldg(p.total_tiles);
   if (tile >= live_tiles) return;

@@ -19,9 +19,9 @@
 // Part of tbe_nbit.cu: included there inside its namespace, after NbitParams.
 #pragma once
 
-constexpr int kNbitBagWarps = 8;
+constexpr int kNbitBagWarps = 2;
 constexpr int kNbitBagThreads = kNbitBagWarps * 32;
-constexpr int kNbitBagCtasPerSm = 6;   // 48 warps per SM at 40 registers (a few spilled words); 5 CTAs measured 6 % slower
+constexpr int kNbitBagCtasPerSm = 24;  // 48 warps per SM at 40 registers (a few spilled words); 40 warps measured 6 % slower
 constexpr int kNbitBagMaxD = 128;
 
 // Tables this kernel takes; everything else (INT2, float rows, wider or oddly aligned rows) stays
