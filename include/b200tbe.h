@@ -63,7 +63,8 @@ typedef enum { B200TBE_OPT_SGD = 0, B200TBE_OPT_ROWWISE_ADAGRAD = 1 } b200tbe_op
 #define B200TBE_DEV_INDEX_OUT_OF_RANGE 1
 #define B200TBE_DEV_OFFSETS_NOT_MONOTONE 2
 #define B200TBE_DEV_UNSUPPORTED_SHAPE 4 /* a table's row is not whole 16-byte vectors */
-#define B200TBE_DEV_WAIT_TIMEOUT 8      /* a bounded wait inside a kernel gave up */
+#define B200TBE_DEV_WAIT_TIMEOUT 8      /* reserved: a bounded wait inside a kernel gave up (no kernel of
+                                           this version waits on anything but its own loads) */
 
 #define B200TBE_MAX_DESTS 16
 #define B200TBE_MAX_JAGGED_DIMS 4
@@ -73,8 +74,7 @@ B200TBE_API int b200tbe_abi_version(void);
 
 /* ------------------------------------------------------------------------------------------------
  * TBE forward over fp32 / fp16 tables (the forward half of
- * torch.ops.fbgemm.split_embedding_codegen_lookup_{sgd,rowwise_adagrad}_function and of
- * torch.ops.fbgemm.dense_embedding_codegen_lookup_function).
+ * torch.ops.fbgemm.split_embedding_codegen_lookup_{sgd,rowwise_adagrad}_function).
  *
  * Bags are table-major: bag (t, b) has id t*B + b and pools rows indices[offsets[id] ..
  * offsets[id+1]) of table t. Row r of table t starts at element weights_offsets[t] + r*D_t of

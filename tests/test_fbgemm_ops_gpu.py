@@ -44,6 +44,63 @@ def test_jagged_ops_match_oracle_bit_for_bit():
     assert np.array_equal(v1.cpu().numpy(), want1)
 
 
+def test_jagged_ops_are_differentiable():
+    """Each copy's gradient is the other copy of the output gradient (bit-exact: the backward passes are
+    the same kernels); the add hands its gradient to y unchanged and to x through dense_to_jagged."""
+    j = workloads.jagged_inputs(96, 20, 32, 3)
+    rng = workloads.rng_for(502)
+    values = rng.standard_normal((j.total_rows, j.D)).astype(np.float32)
+    y = rng.standard_normal((j.B, j.max_L, j.D)).astype(np.float32)
+    w = rng.standard_normal((j.B, j.max_L, j.D)).astype(np.float32)
+    wj = rng.standard_normal((j.total_rows, j.D)).astype(np.float32)
+    off = _dev(j.offsets)
+
+    v = _dev(values).requires_grad_(True)
+    dense = torch.ops.fbgemm.jagged_to_padded_dense(v, [off], [j.max_L], 7.0)
+    assert dense.grad_fn is not None
+    (dense * _dev(w)).sum().backward()
+    assert np.array_equal(v.grad.cpu().numpy(), oracle.dense_to_jagged(w, [j.offsets], j.total_rows))
+
+    d = _dev(y).requires_grad_(True)
+    back, _ = torch.ops.fbgemm.dense_to_jagged(d, [off], j.total_rows)
+    (back * _dev(wj)).sum().backward()
+    assert np.array_equal(d.grad.cpu().numpy(), oracle.jagged_to_padded_dense(wj, [j.offsets], [j.max_L], 0.0))
+
+    x = _dev(values).requires_grad_(True)
+    yy = _dev(y).requires_grad_(True)
+    out = torch.ops.fbgemm.jagged_dense_elementwise_add(x, [off], yy)
+    (out * _dev(w)).sum().backward()
+    assert np.array_equal(yy.grad.cpu().numpy(), w)
+    assert np.array_equal(x.grad.cpu().numpy(), oracle.dense_to_jagged(w, [j.offsets], j.total_rows))
+    # no graph, no node
+    assert torch.ops.fbgemm.jagged_to_padded_dense(_dev(values), [off], [j.max_L], 0.0).grad_fn is None
+
+
+def test_device_status_word_reports_bad_ids_from_the_ops():
+    """The lookup ops range-check ids against hash_size_cumsum; a bad id is skipped and shows up in
+    torch.ops.fbgemm.b200tbe_pop_device_status, which clears the word."""
+    T, E, D, B = 2, 50, 16, 4
+    w = torch.ones(T * E * D, device="cuda")
+    wo = torch.arange(T, device="cuda", dtype=torch.int64) * (E * D)
+    Do = torch.arange(T + 1, device="cuda", dtype=torch.int32) * D
+    hs = torch.arange(T + 1, device="cuda", dtype=torch.int64) * E
+    offsets = torch.arange(T * B + 1, device="cuda", dtype=torch.int64) * 2
+    idx = torch.randint(0, E, (T * B * 2,), device="cuda")
+    e, ei = _empty(), _empty(torch.int32)
+    args = lambda ids: (torch.zeros(1, device="cuda"), w, e, e, ei, wo, Do, T * D, D, hs, 7, ids, offsets, 0, None,
+                        None, ei, False, 0.0, False, 0.0, 0)
+    torch.ops.fbgemm.b200tbe_pop_device_status(w)
+    out = torch.ops.fbgemm.split_embedding_codegen_lookup_sgd_function(*args(idx))
+    assert torch.ops.fbgemm.b200tbe_pop_device_status(w) == 0
+    assert torch.equal(out, torch.full((B, T * D), 2.0, device="cuda"))
+    bad = idx.clone()
+    bad[3] = E                       # one row past the table
+    out = torch.ops.fbgemm.split_embedding_codegen_lookup_sgd_function(*args(bad))
+    assert torch.ops.fbgemm.b200tbe_pop_device_status(w) & 1      # B200TBE_DEV_INDEX_OUT_OF_RANGE
+    assert torch.ops.fbgemm.b200tbe_pop_device_status(w) == 0     # popped
+    assert float(out[1, :D].sum()) == D                           # the bad lookup was skipped, its neighbour pooled
+
+
 def test_ops_reject_cpu_tensors_and_bad_shapes():
     with pytest.raises((RuntimeError, NotImplementedError)):
         torch.ops.fbgemm.jagged_to_padded_dense(torch.zeros(3, 2), [torch.zeros(2, dtype=torch.int64)], [2], 0.0)

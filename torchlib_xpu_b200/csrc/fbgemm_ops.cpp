@@ -261,6 +261,91 @@ Tensor jagged_2d_to_dense(const Tensor& values, const Tensor& offsets, int64_t m
   return jagged_to_padded_dense(values, {offsets}, {max_sequence_length}, 0.0);
 }
 
+// ---- autograd for the jagged ops --------------------------------------------------------------
+// The two copies are each other's transpose: the gradient of jagged_to_padded_dense with respect to
+// values is dense_to_jagged of the output gradient (padding positions receive none), and the
+// gradient of dense_to_jagged with respect to dense is jagged_to_padded_dense of the output
+// gradient with zero padding. jagged_dense_elementwise_add passes its gradient to y unchanged and
+// to x_values through dense_to_jagged. Offsets carry no gradient. The backward passes are the same
+// CUDA kernels, called below the autograd key so that they are not recorded again.
+std::vector<int64_t> max_lengths_of(const Tensor& dense, size_t jagged_dims) {
+  return std::vector<int64_t>(dense.sizes().begin() + 1, dense.sizes().begin() + 1 + jagged_dims);
+}
+
+class JaggedToPaddedDenseFunction : public torch::autograd::Function<JaggedToPaddedDenseFunction> {
+ public:
+  static Variable forward(AutogradContext* ctx, const Tensor& values, const std::vector<Tensor>& offsets,
+                          std::vector<int64_t> max_lengths, double padding_value) {
+    at::AutoDispatchBelowADInplaceOrView guard;
+    ctx->save_for_backward(offsets);
+    ctx->saved_data["total"] = values.size(0);
+    ctx->saved_data["vector"] = values.dim() == 1;
+    return jagged_to_padded_dense(values, offsets, max_lengths, padding_value);
+  }
+  static variable_list backward(AutogradContext* ctx, variable_list grads) {
+    at::AutoDispatchBelowADInplaceOrView guard;
+    const auto offsets = ctx->get_saved_variables();
+    Tensor g = grads[0].contiguous();
+    const bool vec = ctx->saved_data["vector"].toBool();
+    if (vec) g = g.unsqueeze(-1);
+    Tensor gv = std::get<0>(dense_to_jagged(g, offsets, ctx->saved_data["total"].toInt()));
+    if (vec) gv = gv.squeeze(-1);
+    return {gv, Tensor(), Tensor(), Tensor()};
+  }
+};
+
+class DenseToJaggedFunction : public torch::autograd::Function<DenseToJaggedFunction> {
+ public:
+  static Variable forward(AutogradContext* ctx, const Tensor& dense, const std::vector<Tensor>& offsets,
+                          c10::optional<int64_t> total_L) {
+    at::AutoDispatchBelowADInplaceOrView guard;
+    ctx->save_for_backward(offsets);
+    ctx->saved_data["max_lengths"] = max_lengths_of(dense, offsets.size());
+    return std::get<0>(dense_to_jagged(dense, offsets, total_L));
+  }
+  static variable_list backward(AutogradContext* ctx, variable_list grads) {
+    at::AutoDispatchBelowADInplaceOrView guard;
+    const auto offsets = ctx->get_saved_variables();
+    const std::vector<int64_t> ml = ctx->saved_data["max_lengths"].toIntVector();
+    return {jagged_to_padded_dense(grads[0].contiguous(), offsets, ml, 0.0), Tensor(), Tensor()};
+  }
+};
+
+class JaggedDenseAddFunction : public torch::autograd::Function<JaggedDenseAddFunction> {
+ public:
+  static Variable forward(AutogradContext* ctx, const Tensor& x_values, const std::vector<Tensor>& x_offsets,
+                          const Tensor& y) {
+    at::AutoDispatchBelowADInplaceOrView guard;
+    ctx->save_for_backward(x_offsets);
+    ctx->saved_data["total"] = x_values.size(0);
+    return jagged_dense_elementwise_add(x_values, x_offsets, y);
+  }
+  static variable_list backward(AutogradContext* ctx, variable_list grads) {
+    at::AutoDispatchBelowADInplaceOrView guard;
+    const auto offsets = ctx->get_saved_variables();
+    const Tensor g = grads[0].contiguous();
+    return {std::get<0>(dense_to_jagged(g, offsets, ctx->saved_data["total"].toInt())), Tensor(), g};
+  }
+};
+
+Tensor jagged_to_padded_dense_autograd(const Tensor& values, const std::vector<Tensor>& offsets,
+                                       at::IntArrayRef max_lengths, double padding_value) {
+  return JaggedToPaddedDenseFunction::apply(values, offsets, max_lengths.vec(), padding_value);
+}
+std::tuple<Tensor, std::vector<Tensor>> dense_to_jagged_autograd(const Tensor& dense,
+                                                                 const std::vector<Tensor>& offsets,
+                                                                 c10::optional<int64_t> total_L) {
+  return {DenseToJaggedFunction::apply(dense, offsets, total_L), offsets};
+}
+Tensor jagged_dense_elementwise_add_autograd(const Tensor& x_values, const std::vector<Tensor>& x_offsets,
+                                             const Tensor& y) {
+  return JaggedDenseAddFunction::apply(x_values, x_offsets, y);
+}
+Tensor jagged_2d_to_dense_autograd(const Tensor& values, const Tensor& offsets, int64_t max_sequence_length) {
+  return JaggedToPaddedDenseFunction::apply(values, std::vector<Tensor>{offsets},
+                                            std::vector<int64_t>{max_sequence_length}, 0.0);
+}
+
 // ---- permute_2D_sparse_data -----------------------------------------------------------------------
 // lengths is [T, B], indices (and weights) hold the T rows' ids one row after the other; row j of
 // the result is row permute[j] of the input (rows may repeat or be left out, so the result can be
@@ -776,8 +861,13 @@ TORCH_LIBRARY_IMPL(fbgemm, CUDA, m) {
   m.impl("b200tbe_pop_device_status", TORCH_FN(pop_device_status));
 }
 
-// The training lookups carry their own autograd node, so they sit on the Autograd key.
+// The training lookups and the jagged ops carry their own autograd nodes, so they also sit on the
+// Autograd key (the jagged ops' CUDA registrations above are what those nodes call).
 TORCH_LIBRARY_IMPL(fbgemm, AutogradCUDA, m) {
+  m.impl("jagged_to_padded_dense", TORCH_FN(jagged_to_padded_dense_autograd));
+  m.impl("dense_to_jagged", TORCH_FN(dense_to_jagged_autograd));
+  m.impl("jagged_dense_elementwise_add", TORCH_FN(jagged_dense_elementwise_add_autograd));
+  m.impl("jagged_2d_to_dense", TORCH_FN(jagged_2d_to_dense_autograd));
   m.impl("split_embedding_codegen_lookup_rowwise_adagrad_function",
          TORCH_FN(split_embedding_codegen_lookup_rowwise_adagrad_function));
   m.impl("split_embedding_codegen_lookup_sgd_function",

@@ -36,10 +36,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1)
     tbe_forward_kernel(const __grid_constant__ FwdParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   WarpRing* rings = reinterpret_cast<WarpRing*>(smem_raw);
-  stream_init_rings(rings);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   WarpRing& ring = rings[warp];
-  uint32_t phases = 0;
   const StreamBags bags{p.indices, p.offsets, p.per_sample_weights, p.status, p.pooling_mode};
   const int64_t stride_units = static_cast<int64_t>(gridDim.x) * kStreamWarps;
   for (int64_t unit = static_cast<int64_t>(blockIdx.x) * kStreamWarps + warp; unit < p.num_units;
@@ -61,8 +59,7 @@ __global__ void __launch_bounds__(kStreamThreads, 1)
     if (streamable) {
       const StreamTable tab{table, row_bytes, static_cast<int>(row_bytes), D >> 2, num_rows};
       const StreamOut<OT> out{outputs, p.output_stride, col, p.rows_per_dest};
-      if (!stream_unit<FloatRow<WT>, OT, IndexT, kVPL>(bags, tab, out, bag0, b0, nb, ring, phases, lane))
-        return;
+      stream_unit<FloatRow<WT>, OT, IndexT, kVPL>(bags, tab, out, bag0, b0, nb, ring, lane);
     } else {
       pool_unit_generic<OT, IndexT>(p.indices, p.offsets, p.per_sample_weights, p.status,
                                     p.pooling_mode, sizeof(WT) == 4 ? B200TBE_FP32 : B200TBE_FP16,
@@ -72,8 +69,14 @@ __global__ void __launch_bounds__(kStreamThreads, 1)
   }
 }
 
+// CTAs of kW warps per SM: 64 warps of fp16 rows, 48 of fp32 rows, at most 32 CTAs.
+constexpr int bag_ctas_per_sm(size_t elem_bytes, int kW) {
+  const int warps = (elem_bytes == 4 ? kBagCtasPerSm - 2 : kBagCtasPerSm) * kBagWarps;
+  return warps / kW > 32 ? 32 : warps / kW;
+}
+
 template <typename WT, typename OT, typename IndexT, bool kWeighted, int kW>
-__global__ void __launch_bounds__(kW * 32, (sizeof(WT) == 4 ? kBagCtasPerSm - 2 : kBagCtasPerSm) * kBagWarps / kW)
+__global__ void __launch_bounds__(kW * 32, bag_ctas_per_sm(sizeof(WT), kW))
     tbe_forward_bags_kernel(const __grid_constant__ FwdParams p) {
   const int lane = threadIdx.x & 31;
   const int64_t bag = static_cast<int64_t>(blockIdx.x) * kW + (threadIdx.x >> 5);

@@ -72,10 +72,8 @@ __global__ void __launch_bounds__(kStreamThreads, 1)
     tbe_nbit_forward_kernel(const __grid_constant__ NbitParams p) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   WarpRing* rings = reinterpret_cast<WarpRing*>(smem_raw);
-  stream_init_rings(rings);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   WarpRing& ring = rings[warp];
-  uint32_t phases = 0;
   const StreamBags bags{p.indices, p.offsets, p.per_sample_weights, p.status, p.pooling_mode};
   const int64_t stride_units = static_cast<int64_t>(gridDim.x) * kStreamWarps;
   for (int64_t unit = static_cast<int64_t>(blockIdx.x) * kStreamWarps + warp; unit < p.num_units;
@@ -101,25 +99,24 @@ __global__ void __launch_bounds__(kStreamThreads, 1)
                             (reinterpret_cast<uintptr_t>(table) & 15) == 0 &&
                             copy_bytes <= row_stride && copy_bytes <= kStageBytes &&
                             (D >> 2) <= 32 * kVPL;
-    bool ok = true;
     if (streamable) {
       const StreamTable tab{table, row_stride, static_cast<int>(copy_bytes), D >> 2, num_rows};
       const StreamOut<OT> out{outputs, p.output_stride, col, p.rows_per_dest};
       switch (ty) {
         case B200TBE_INT8:
-          ok = stream_unit<QuantRow<8>, OT, IndexT, kVPL>(bags, tab, out, bag0, b0, nb, ring, phases, lane);
+          stream_unit<QuantRow<8>, OT, IndexT, kVPL>(bags, tab, out, bag0, b0, nb, ring, lane);
           break;
         case B200TBE_INT4:
-          ok = stream_unit<QuantRow<4>, OT, IndexT, kVPL>(bags, tab, out, bag0, b0, nb, ring, phases, lane);
+          stream_unit<QuantRow<4>, OT, IndexT, kVPL>(bags, tab, out, bag0, b0, nb, ring, lane);
           break;
         case B200TBE_INT2:
-          ok = stream_unit<QuantRow<2>, OT, IndexT, kVPL>(bags, tab, out, bag0, b0, nb, ring, phases, lane);
+          stream_unit<QuantRow<2>, OT, IndexT, kVPL>(bags, tab, out, bag0, b0, nb, ring, lane);
           break;
         case B200TBE_FP16:
-          ok = stream_unit<FloatRow<__half>, OT, IndexT, kVPL>(bags, tab, out, bag0, b0, nb, ring, phases, lane);
+          stream_unit<FloatRow<__half>, OT, IndexT, kVPL>(bags, tab, out, bag0, b0, nb, ring, lane);
           break;
         default:
-          ok = stream_unit<FloatRow<float>, OT, IndexT, kVPL>(bags, tab, out, bag0, b0, nb, ring, phases, lane);
+          stream_unit<FloatRow<float>, OT, IndexT, kVPL>(bags, tab, out, bag0, b0, nb, ring, lane);
           break;
       }
     } else {
@@ -127,7 +124,6 @@ __global__ void __launch_bounds__(kStreamThreads, 1)
                                     p.pooling_mode, ty, table, row_stride, D, num_rows, outputs,
                                     p.output_stride, col, p.rows_per_dest, bag0, b0, nb, lane);
     }
-    if (!ok) return;
   }
 }
 

@@ -1,36 +1,29 @@
-// Streaming gather engine shared by the pooled-forward kernels.
+// Streaming gather engine: the pooled lookup for rows that do not fit a register gather (float rows
+// wider than 512 bytes; INT2, float and wide rows of the quantised lookup) and the backward's run
+// reduction for rows of more than 512 elements.
 //
 // A gather of embedding rows is bound by memory latency unless enough bytes are in flight: a
-// random 80..512-byte row costs an L2 or HBM round trip of about a microsecond, so an SM needs on
+// random 80..4096-byte row costs an L2 or HBM round trip of about a microsecond, so an SM needs on
 // the order of 100 KB outstanding to keep its share of the memory system busy. Registers cannot
-// hold that, shared memory can. Each warp therefore owns a private ring of kStages stages in
-// shared memory. To fill a stage, every lane issues ONE bulk asynchronous copy (cp.async.bulk,
-// global -> shared, completion counted in bytes on an mbarrier) for the whole row of one lookup,
-// so a single warp instruction puts up to 32 rows in flight and costs no registers. The warp
-// then consumes stages in order: one row per instruction, lane v taking elements [4v, 4v+4) of the
-// row from shared memory, accumulating in fp32 registers, and writing a bag's pooled vector when
-// the stream of lookups crosses the bag's end. Two stages are in flight while a third is being
-// consumed; 16 warps x 2 stages x 4 KB = 128 KB in flight per SM.
+// hold that for wide rows, shared memory can. Each warp therefore owns a private ring of kStages
+// stages in shared memory. A stage is filled with cp.async (16 bytes per lane, 32 consecutive
+// chunks per instruction, through L1 so that the hottest rows hit there; the copies cost no
+// registers and complete in order per thread, tracked by cp.async groups). The warp then consumes
+// stages in order: one row per instruction, lane v taking elements [4v, 4v+4) of the row from shared
+// memory, accumulating in fp32 registers, and writing a bag's pooled vector when the stream of
+// lookups crosses the bag's end. Two stages are in flight while a third is being consumed;
+// 16 warps x 2 stages x 4 KB = 128 KB in flight per SM.
+// (One cp.async.bulk per row was measured instead of cp.async: a bulk copy issued by 32 lanes
+// executes as 32 separate copies with about 20 instructions of set-up each, slower for rows of a few
+// hundred bytes; it is not built.)
 //
 // Work is cut into units of a few consecutive bags of one table (so a unit's lookups are one
 // contiguous range of the index array and its table parameters are warp-uniform); a persistent
 // grid of one CTA per SM strides over the units, which keeps all SMs on the same table at the same
-// time and lets repeated rows hit in L2.
-//
-// Every wait on an mbarrier is bounded: a warp that gives up records B200TBE_DEV_WAIT_TIMEOUT in
-// the status word and stops; nothing spins forever.
+// time and lets repeated rows hit in L2. Nothing in the engine waits on another warp.
 #pragma once
 
 #include "tbe_pool.cuh"
-
-// Two ways to fill a ring stage. Default: cp.async (16 bytes per lane, 32 consecutive chunks per
-// instruction, through L1 so that the hottest rows hit there). -DB200TBE_STREAM_BULK selects one
-// cp.async.bulk per row instead; measured on B200 it is slower for rows of a few hundred bytes,
-// because a bulk copy issued by 32 lanes executes as 32 separate instructions (one TMA instruction
-// per row, about 20 warp instructions of overhead each).
-#ifndef B200TBE_STREAM_BULK
-#define B200TBE_STREAM_LDGSTS 1
-#endif
 
 namespace b200tbe {
 
@@ -38,11 +31,6 @@ constexpr int kStreamWarps = 16;
 constexpr int kStreamThreads = kStreamWarps * 32;
 constexpr int kStages = 3;
 constexpr int kStageBytes = 4096;
-// Bounded mbarrier wait: each try suspends the thread in hardware for up to kWaitHintNs (it wakes
-// as soon as the phase completes), so a waiting warp issues almost no instructions; after
-// kWaitSpins tries (about two seconds) the wait gives up.
-constexpr int kWaitSpins = 1 << 17;
-constexpr uint32_t kWaitHintNs = 16384;
 
 struct WarpRing {
   alignas(128) char rows[kStages][kStageBytes];
@@ -50,61 +38,12 @@ struct WarpRing {
   float2 mult[kStages][32];   // per row {multiplier, bias term} of the stage being consumed
   uint32_t valid[kStages];
   uint32_t pad_;
-  unsigned long long bar[kStages];
 };
 
 constexpr size_t kStreamSmemBytes = sizeof(WarpRing) * kStreamWarps;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-
-__device__ __forceinline__ void mbar_init(unsigned long long* bar, int count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(unsigned long long* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
-               "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(unsigned long long* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity), "r"(kWaitHintNs)
-      : "memory");
-  return ok != 0;
-}
-// Returns false when the wait gave up.
-__device__ __forceinline__ bool mbar_wait_bounded(unsigned long long* bar, uint32_t parity) {
-  for (int i = 0; i < kWaitSpins; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
-  return false;
-}
-__device__ __forceinline__ void fence_proxy_async_smem() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-__device__ __forceinline__ void bulk_copy_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes,
-                                              unsigned long long* bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-          smem_u32(smem_dst)),
-      "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar))
-      : "memory");
-}
-
-// Call once per CTA before any warp streams (all threads).
-__device__ __forceinline__ void stream_init_rings(WarpRing* rings) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (lane < kStages) mbar_init(&rings[warp].bar[lane], 1);
-  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  fence_proxy_async_smem();
-  __syncthreads();
 }
 
 // What a unit's table looks like to the engine (warp-uniform).
@@ -317,13 +256,12 @@ __device__ __forceinline__ void consume(Acc4 (&acc)[kVPL], float& bias_acc, uint
 }
 
 // Pools the bags [b0, b0 + nb) of table t (nb <= 31): lookups offsets[t*B+b0] .. offsets[t*B+b0+nb).
-// `phases` holds one parity bit per ring stage and lives across units. Returns false if a wait
-// timed out (the caller must stop using the ring). Positions inside the unit are 32-bit offsets
-// from the unit's first lookup (a unit is at most 31 bags long).
+// Positions inside the unit are 32-bit offsets from the unit's first lookup (a unit is at most 31
+// bags long).
 template <typename Row, typename OT, typename IndexT, int kVPL>
-__device__ __forceinline__ bool stream_unit(const StreamBags& bags, const StreamTable& tab,
+__device__ __forceinline__ void stream_unit(const StreamBags& bags, const StreamTable& tab,
                                             const StreamOut<OT>& out, int64_t bag0, int b0, int nb,
-                                            WarpRing& ring, uint32_t& phases, int lane) {
+                                            WarpRing& ring, int lane) {
   // lane j holds the start of bag j of the unit (j = nb: the unit's end), relative to the unit
   const int64_t my_off64 = lane <= nb ? load_index<IndexT>(bags.offsets, bag0 + lane) : 0;
   const int64_t p_begin = __shfl_sync(kFullMask, my_off64, 0);
@@ -383,13 +321,11 @@ __device__ __forceinline__ bool stream_unit(const StreamBags& bags, const Stream
   // that many stages ahead of the row copies, which run kStages - 1 stages ahead of consumption
   constexpr int kIdxAhead = 3;
   int64_t idx_q[kIdxAhead] = {};
-#ifdef B200TBE_STREAM_LDGSTS
   const int chunks = tab.copy_bytes >> 4;                       // 16-byte chunks per row
   const int copy_iters = (rows_per_stage * chunks + 31) >> 5;    // warp instructions per stage
   const int chunk_shift = (chunks & (chunks - 1)) == 0 && chunks <= 32 ? __ffs(chunks) - 1 : -1;
   const int lane_row0 = lane / chunks, lane_chunk0 = lane - lane_row0 * chunks;
   const int row_step = 32 / chunks, chunk_step = 32 - row_step * chunks;
-#endif
   int issue_pos = lane;   // position (relative) this lane issues in the next stage to be issued
   int issue_slot = 0;
   auto load_idx = [&](int pos) -> int64_t {
@@ -412,7 +348,6 @@ __device__ __forceinline__ bool stream_unit(const StreamBags& bags, const Stream
     }
     const uint32_t vmask = __ballot_sync(kFullMask, ok);
     if (weighted) ring.weights[slot][lane] = in_stage ? __ldg(psw_base + pos) : 0.f;
-#ifdef B200TBE_STREAM_LDGSTS
     if (lane == 0) ring.valid[slot] = vmask;
     // lane i knows where row i of the stage lives (as a 16-byte chunk number inside the table);
     // the copy itself runs over the stage buffer in 16-byte chunks, 32 consecutive chunks per
@@ -483,15 +418,6 @@ __device__ __forceinline__ bool stream_unit(const StreamBags& bags, const Stream
       }
     }
     asm volatile("cp.async.commit_group;" ::: "memory");
-#else
-    if (lane == 0) {
-      ring.valid[slot] = vmask;
-      mbar_arrive_expect_tx(&ring.bar[slot], __popc(vmask) * static_cast<uint32_t>(tab.copy_bytes));
-    }
-    if (ok)
-      bulk_copy_g2s(ring.rows[slot] + lane * tab.copy_bytes, tab.base + idx * tab.stride,
-                    static_cast<uint32_t>(tab.copy_bytes), &ring.bar[slot]);
-#endif
   };
 
 #pragma unroll
@@ -501,9 +427,7 @@ __device__ __forceinline__ bool stream_unit(const StreamBags& bags, const Stream
     if (issued < num_stages) {
       issue();
     } else {
-#ifdef B200TBE_STREAM_LDGSTS
       asm volatile("cp.async.commit_group;" ::: "memory");
-#endif
     }
   }
   __syncwarp();
@@ -512,25 +436,13 @@ __device__ __forceinline__ bool stream_unit(const StreamBags& bags, const Stream
   int pos0 = 0;
   for (int stage = 0; stage < num_stages; ++stage) {
     if (stage + kStages - 1 < num_stages) {
-      // the slot being refilled was read by ordinary loads in the previous iteration
-      fence_proxy_async_smem();
       issue();
     } else {
-#ifdef B200TBE_STREAM_LDGSTS
       asm volatile("cp.async.commit_group;" ::: "memory");
-#endif
     }
     __syncwarp();
-#ifdef B200TBE_STREAM_LDGSTS
     asm volatile("cp.async.wait_group %0;" ::"n"(kStages - 1) : "memory");
     __syncwarp();
-#else
-    if (!mbar_wait_bounded(&ring.bar[slot], (phases >> slot) & 1u)) {
-      if (lane == 0) atomicOr(bags.status, B200TBE_DEV_WAIT_TIMEOUT);
-      return false;
-    }
-    phases ^= 1u << slot;
-#endif
     const uint32_t vmask = ring.valid[slot];
     const int nr = total - pos0 < rows_per_stage ? total - pos0 : rows_per_stage;
     const uint32_t rows_addr = smem_u32(ring.rows[slot]);
@@ -579,7 +491,6 @@ __device__ __forceinline__ bool stream_unit(const StreamBags& bags, const Stream
     slot = slot + 1 == kStages ? 0 : slot + 1;
   }
   while (cur_bag < nb) flush();
-  return true;
 }
 
 // Any row layout, alignment or width: the bags of a unit one at a time, 128 columns per pass,
