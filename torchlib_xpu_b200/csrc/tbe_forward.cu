@@ -69,18 +69,11 @@ __global__ void __launch_bounds__(kStreamThreads, 1)
   }
 }
 
-// CTAs of kW warps per SM: 64 warps of fp16 rows, 48 of fp32 rows, at most 32 CTAs.
-constexpr int bag_ctas_per_sm(size_t elem_bytes, int kW) {
-  const int warps = (elem_bytes == 4 ? kBagCtasPerSm - 2 : kBagCtasPerSm) * kBagWarps;
-  return warps / kW > 32 ? 32 : warps / kW;
-}
-
-template <typename WT, typename OT, typename IndexT, bool kWeighted, int kW>
-__global__ void __launch_bounds__(kW * 32, bag_ctas_per_sm(sizeof(WT), kW))
+template <typename WT, typename OT, typename IndexT, bool kWeighted>
+__global__ void __launch_bounds__(32, kBagCtasPerSm)
     tbe_forward_bags_kernel(const __grid_constant__ FwdParams p) {
-  const int lane = threadIdx.x & 31;
-  const int64_t bag = static_cast<int64_t>(blockIdx.x) * kW + (threadIdx.x >> 5);
-  if (bag >= static_cast<int64_t>(p.T) * p.B) return;
+  const int lane = threadIdx.x;
+  const int64_t bag = blockIdx.x;
   const int t = static_cast<int>(bag / p.B);
   const int b = static_cast<int>(bag - static_cast<int64_t>(t) * p.B);
   const int D_begin = __ldg(p.D_offsets + t);
@@ -106,21 +99,12 @@ __global__ void __launch_bounds__(kW * 32, bag_ctas_per_sm(sizeof(WT), kW))
 template <typename WT, typename OT, typename IndexT>
 int launch_bags(const FwdParams& d, cudaStream_t stream) {
   const int64_t bags = static_cast<int64_t>(d.T) * d.B;
-  // Warps per CTA: a CTA holds its slot until its longest bag is done, so small CTAs keep more warps
-  // busy (bags differ in length by 50 x). fp16 rows: 4 warps (16 CTAs x 4 = 64 warps per SM; 8 warps per
-  // CTA measured 6 % slower, 2 warps 4 % slower, 1 warp -- 32 CTAs per SM at most -- 27 % slower on the bench
-  // step). fp32 rows (48 warps per SM by registers): 2 warps; a grid too small to fill the GPU several times
-  // over runs fastest with one warp per CTA (config 1: 0.045 ms against 0.049 and 0.053).
   if (bags > 0x7fffffff) return B200TBE_ERR_TOO_LARGE;
-  if (d.per_sample_weights != nullptr) {
-    tbe_forward_bags_kernel<WT, OT, IndexT, true, 4><<<static_cast<unsigned>((bags + 3) / 4), 128, 0, stream>>>(d);
-  } else if (sizeof(WT) == 2) {
-    tbe_forward_bags_kernel<WT, OT, IndexT, false, 4><<<static_cast<unsigned>((bags + 3) / 4), 128, 0, stream>>>(d);
-  } else if (bags < int64_t{kNumSMs} * 32 * 8) {
-    tbe_forward_bags_kernel<WT, OT, IndexT, false, 1><<<static_cast<unsigned>(bags), 32, 0, stream>>>(d);
-  } else {
-    tbe_forward_bags_kernel<WT, OT, IndexT, false, 2><<<static_cast<unsigned>((bags + 1) / 2), 64, 0, stream>>>(d);
-  }
+  const unsigned grid = static_cast<unsigned>(bags);
+  if (d.per_sample_weights != nullptr)
+    tbe_forward_bags_kernel<WT, OT, IndexT, true><<<grid, 32, 0, stream>>>(d);
+  else
+    tbe_forward_bags_kernel<WT, OT, IndexT, false><<<grid, 32, 0, stream>>>(d);
   return launch_status();
 }
 
