@@ -98,6 +98,50 @@ def test_forward_flags_out_of_range_indices():
     np.testing.assert_allclose(got.cpu().numpy(), want, rtol=RTOL_FP32, atol=1e-7)
 
 
+@pytest.mark.parametrize("wdtype,weighted,pooling,idx_dtype,B", [
+    (np.float16, False, oracle.SUM, np.int64, 12001),     # groups of 3 bags, the last group short
+    (np.float16, True, oracle.MEAN, np.int32, 30000),     # groups of 7
+    (np.float32, False, oracle.MEAN, np.int32, 30011),
+    (np.float32, True, oracle.SUM, np.int64, 12001),
+])
+def test_forward_groups_of_bags(wdtype, weighted, pooling, idx_dtype, B):
+    """A grid of more than about 47 k bags gives every warp a GROUP of consecutive bags to pool as one
+    stream of lookups. Bags of 0 to 40 lookups, runs of empty bags (a third of all, the tail of a table
+    included), rows of 16 to 512 bytes and one that is not a whole vector, ids out of range."""
+    rng = workloads.rng_for(210 + B)
+    Ds = [128, 64, 32, 8, 20, 4] if wdtype == np.float32 else [128, 64, 32, 8, 20, 256]
+    rows = [3000, 2000, 1000, 500, 300, 600]
+    T = len(Ds)
+    W, wo, Do = helpers.float_tables(rng, rows, Ds, wdtype, -1.0, 1.0)
+    lengths, _, _ = helpers.ragged_bags(rng, T, B, rows, 0, 40, empty_fraction=0.33)
+    lengths[B - 40:B] = 0                  # a table that ends in empty bags
+    lengths[2 * B:2 * B + 64] = 0          # whole groups without a lookup
+    lengths[-5:] = 0
+    offsets = np.zeros(T * B + 1, dtype=np.int64)
+    np.cumsum(lengths, out=offsets[1:])
+    indices = np.zeros(int(offsets[-1]), dtype=np.int64)
+    for t in range(T):
+        a, b = int(offsets[t * B]), int(offsets[(t + 1) * B])
+        indices[a:b] = rng.integers(0, rows[t], size=b - a, dtype=np.int64)
+    bad_at = rng.choice(indices.size, size=200, replace=False)
+    bad = indices.copy()
+    bad[bad_at[:100]] = 5000               # past every table
+    bad[bad_at[100:]] = -1
+    psw = rng.random(indices.size).astype(np.float32) if weighted else None
+    got, status = _run(W, wo, Do, rows, B, bad, offsets, psw, pooling, torch.float32, idx_dtype=idx_dtype)
+    assert status & cabi.DEV_INDEX_OUT_OF_RANGE
+    # flagged lookups contribute nothing (MEAN still divides by the bag's length)
+    keep = np.ones(indices.size, dtype=np.float32)
+    keep[bad_at] = 0.0
+    ty = oracle.FP32 if wdtype == np.float32 else oracle.FP16
+    want = oracle.tbe_forward(W, ty, wo, Do, B, np.where(keep > 0, indices, 0), offsets,
+                              keep if psw is None else psw * keep, pooling)
+    if wdtype == np.float32:
+        np.testing.assert_allclose(got.cpu().numpy(), want, rtol=RTOL_FP32, atol=ATOL_FP32_UNIT)
+    else:
+        np.testing.assert_allclose(got.cpu().numpy(), want, rtol=RTOL_FP16, atol=ATOL_FP16)
+
+
 def test_forward_empty_batch_and_bad_args():
     z = torch.zeros(1, dtype=torch.int64, device="cuda")
     out = cabi.forward(torch.zeros(4, device="cuda"), z, torch.zeros(2, dtype=torch.int32, device="cuda"),

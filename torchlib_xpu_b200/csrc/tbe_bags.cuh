@@ -1,11 +1,11 @@
-// One warp per bag: the pooled-lookup engine for rows that fit one load instruction per group.
+// One warp per bag, or per group of consecutive bags: the pooled-lookup engine for rows that fit one
+// load instruction per lane group.
 //
-// A plain grid of bags at few registers per thread (up to 64 warps per SM), so that enough
-// independent row loads are in flight to cover HBM / L2 latency and the hardware's CTA scheduling
-// balances the load. Measured on B200 this simple shape beats both a persistent software-pipelined
-// variant and the shared-memory ring engine of tbe_stream.cuh. The bag's ids are read 32 at a time
-// with one coalesced load and handed out by shuffle as 32-bit row numbers; a row is fetched by a
-// group of gs lanes, so one load instruction brings 32/gs rows; loads allocate in L1, where the
+// A plain grid of one-warp CTAs, so that enough independent row loads are in flight to cover HBM /
+// L2 latency and the hardware's CTA scheduling balances the load. Measured on B200 this shape beats
+// both a persistent variant and the shared-memory ring engine of tbe_stream.cuh. Ids are read 32 at
+// a time with one coalesced load and handed out by shuffle as 32-bit row numbers; a row is fetched
+// by a group of gs lanes, so one load instruction brings 32/gs rows; loads allocate in L1, where the
 // hottest rows of a skewed id stream hit.
 // gs = row bytes / 16 rounded up to a power of two (16 for D = 128 fp16); fp16 elements are added to
 // the fp32 accumulators with the mixed-precision add of sm_100.
@@ -201,6 +201,162 @@ __device__ __forceinline__ void pool_float_bag(const BagLaunch<OT>& p, const cha
 #pragma unroll
     for (int e = 0; e < kE; e += 4) store_pooled<OT, 4>(dst + e, r + e);
   }
+}
+
+// Pools bags [bag0, bag0 + nb), nb <= 32, of one table (bag0 = t * B + b0) as ONE stream of lookups:
+// the bags' ids are consecutive in `indices`, so the warp walks them 32 ids and kLoads load
+// instructions at a time whatever the bags' lengths, and closes a bag -- sum over the row groups,
+// store -- at the step that holds its last lookup. Against one bag per warp this keeps every load
+// round full (a bag of 20 lookups fills 20 of a round's rows) and pays the offsets -> ids -> rows
+// latency chain once per group instead of once per bag: the next 32 ids are requested before the
+// current ones' rows.
+template <typename WT, typename OT, typename IndexT, bool kWeighted>
+__device__ __forceinline__ void pool_float_bags(const BagLaunch<OT>& p, const char* table, int row_bytes,
+                                                int64_t num_rows, int64_t col, int64_t bag0, int b0, int nb,
+                                                int lane) {
+  constexpr int kE = Vec16<WT>::kE;
+  constexpr int kLoads = kBagLoads;
+  // lane i: end of bag i relative to the group's first lookup, made monotone and clamped to 31 bits
+  const int64_t begin = load_index<IndexT>(p.offsets, bag0);
+  int my_end = 0;
+  if (lane < nb) {
+    const int64_t e = load_index<IndexT>(p.offsets, bag0 + lane + 1) - begin;
+    my_end = e < 0 ? 0 : (e > 0x7fffffff ? 0x7fffffff : static_cast<int>(e));
+  }
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int below = __shfl_up_sync(kFullMask, my_end, o);
+    if (lane >= o && below > my_end) my_end = below;
+  }
+  const int total = __shfl_sync(kFullMask, my_end, nb - 1);
+  const IndexT* idx = reinterpret_cast<const IndexT*>(p.indices) + begin;
+  const float* psw = kWeighted ? p.per_sample_weights + begin : nullptr;
+  const int vecs = row_bytes >> 4;
+  const int gs = lanes_per_row(vecs);
+  const int gshift = __ffs(gs) - 1;
+  const int G = 32 >> gshift;            // rows per load instruction
+  const int h = lane >> gshift;          // this lane's group
+  const int v = lane & (gs - 1);         // this lane's vector inside the row
+  const bool active = v < vecs;
+  const char* lane_base = table + (v << 4);
+  // lanes beyond the row's last vector (rows that are not a power of two of vectors) re-read the
+  // last one in the test-free rounds; their sums are never stored
+  const char* lane_any = table + ((active ? v : vecs - 1) << 4);
+  const int64_t row_limit = num_rows >= 0 ? num_rows : int64_t{0xffffffff};
+  const bool mean = p.pooling_mode == B200TBE_POOL_MEAN;
+  const int rpd = static_cast<int>(p.rows_per_dest);
+
+  float acc[kE];
+#pragma unroll
+  for (int e = 0; e < kE; ++e) acc[e] = 0.f;
+  int cur = 0;                                              // bag being summed (warp-uniform)
+  int cur_start = 0;
+  int cur_end = __shfl_sync(kFullMask, my_end, 0);
+
+  // closes bag `cur`: its sum is spread over the row groups
+  auto close_bag = [&]() {
+    for (int o = gs; o < 32; o <<= 1) {
+#pragma unroll
+      for (int e = 0; e < kE; ++e) acc[e] += __shfl_xor_sync(kFullMask, acc[e], o);
+    }
+    if (h == 0 && active) {
+      const int len = cur_end - cur_start;
+      const float scale = (mean && len > 0) ? 1.f / static_cast<float>(len) : 1.f;
+      const int b = b0 + cur;
+      const int dest = b / rpd;
+      OT* dst = p.outputs[dest] + static_cast<int64_t>(b - dest * rpd) * p.output_stride + col + v * kE;
+      float r[kE];
+#pragma unroll
+      for (int e = 0; e < kE; ++e) r[e] = acc[e] * scale;
+#pragma unroll
+      for (int e = 0; e < kE; e += 4) store_pooled<OT, 4>(dst + e, r + e);
+    }
+#pragma unroll
+    for (int e = 0; e < kE; ++e) acc[e] = 0.f;
+    ++cur;
+    cur_start = cur_end;
+    cur_end = __shfl_sync(kFullMask, my_end, cur & 31);
+  };
+
+  IndexT next_id = 0;
+  float next_w = 1.f;
+  if (lane < total) {
+    next_id = __ldg(idx + lane);
+    if (kWeighted) next_w = __ldg(psw + lane);
+  }
+  for (int c = 0; c < total; c += 32) {
+    const int n = total - c < 32 ? total - c : 32;
+    // this lane's row id; ids do not fit 32 bits only in tables no memory holds
+    uint32_t my_row = kNoRow;
+    const float my_w = next_w;
+    if (lane < n) {
+      const int64_t i = static_cast<int64_t>(next_id);
+      if (i < 0 || i >= row_limit) {
+        if (p.status != nullptr) atomicOr(p.status, B200TBE_DEV_INDEX_OUT_OF_RANGE);
+      } else {
+        my_row = static_cast<uint32_t>(i);
+      }
+    }
+    if (c + 32 + lane < total) {
+      next_id = __ldg(idx + c + 32 + lane);
+      if (kWeighted) next_w = __ldg(psw + c + 32 + lane);
+    }
+    const uint32_t bad = __ballot_sync(kFullMask, my_row == kNoRow);   // lanes >= n included
+    const int n_clean = bad == 0 ? 32 : __ffs(bad) - 1;                // rows [0, n_clean) are all good
+    const int round_rows = G * kLoads;
+    for (int j = 0; j < n; j += round_rows) {
+      uint4 x[kLoads];
+      float w[kLoads];
+      if (j + round_rows <= n_clean) {
+        // every row of the round exists and is in range: loads without a test
+#pragma unroll
+        for (int u = 0; u < kLoads; ++u) {
+          const int rr = j + u * G + h;
+          const uint32_t row = __shfl_sync(kFullMask, my_row, rr);
+          if (kWeighted) w[u] = __shfl_sync(kFullMask, my_w, rr);
+          x[u] = ldg_cached16(lane_any + static_cast<uint64_t>(row) * static_cast<uint32_t>(row_bytes));
+        }
+      } else {
+#pragma unroll
+        for (int u = 0; u < kLoads; ++u) {
+          const int rr = j + u * G + h;
+          const uint32_t row = __shfl_sync(kFullMask, my_row, rr & 31);
+          if (kWeighted) w[u] = __shfl_sync(kFullMask, my_w, rr & 31);
+          x[u] = make_uint4(0u, 0u, 0u, 0u);  // +0.0 in either type: adding it changes nothing
+          if (rr < n && row != kNoRow && active)
+            x[u] = ldg_cached16(lane_base + static_cast<uint64_t>(row) * static_cast<uint32_t>(row_bytes));
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kLoads; ++u) {
+        const int step = c + j + u * G;          // lookups [step, step + G) of the stream
+        if (step + G < cur_end) {                // all of them inside the open bag, which goes on
+          if (kWeighted) {
+            Vec16<WT>::fma(acc, x[u], w[u]);
+          } else {
+            Vec16<WT>::add(acc, x[u]);
+          }
+        } else if (j + u * G < n) {          // (a round of more than 32 rows reaches past the ids at hand)
+          // a bag ends in this step: every row goes to the bag that holds it, bags close in order
+          const int q = step + h;
+          bool pending = true;
+          while (cur < nb) {
+            if (pending && q < cur_end) {
+              if (kWeighted) {
+                Vec16<WT>::fma(acc, x[u], w[u]);
+              } else {
+                Vec16<WT>::add(acc, x[u]);
+              }
+              pending = false;
+            }
+            if (step + G < cur_end) break;
+            close_bag();
+          }
+        }
+      }
+    }
+  }
+  while (cur < nb) close_bag();   // bags without lookups at the group's end (or a group without any)
 }
 
 }  // namespace b200tbe
