@@ -126,16 +126,6 @@ __global__ void __launch_bounds__(32, kBagCtasPerSm)
                                              p.output_col_offset + D_begin, bag0, b0, nb, lane);
 }
 
-// Bags per warp. A warp that walks a group of bags as one stream keeps its load rounds full and reads
-// ids ahead, which is worth up to 30 % (64-table fp16 step: 3.36 ms one bag per warp, 2.79 / 2.56 /
-// 2.44 / 2.40 ms for groups of 4 / 8 / 16 / 32), as long as the grid still fills the GPU's 148 x 32
-// warp slots about five times over (26 tables x 8192 bags: 0.184 ms for groups of 6 to 10, 0.197 for
-// 15, 0.221 for 32, 0.211 one bag per warp); a grid smaller than that runs one bag per warp.
-int bag_group_for(int64_t bags) {
-  const int64_t per_slot = bags / (int64_t{kNumSMs} * kBagCtasPerSm * 5);
-  return per_slot < 1 ? 1 : (per_slot > 32 ? 32 : static_cast<int>(per_slot));
-}
-
 template <typename WT, typename OT, typename IndexT>
 int launch_bags(const FwdParams& d0, cudaStream_t stream) {
   const int64_t bags = static_cast<int64_t>(d0.T) * d0.B;

@@ -1,6 +1,6 @@
 // Quantised-inference lookup for the common tables: INT8 and INT4 rows of at most 128 elements.
 //
-// One warp per bag in a plain grid, no shared memory. A row is {fp16 scale, fp16 bias} followed by
+// One warp per group of consecutive bags in a plain grid, no shared memory. A row is {fp16 scale, fp16 bias} followed by
 // the codes, so the codes start 4 bytes into a 16-byte aligned row: they cannot be fetched with
 // aligned 16-byte vectors without dragging the header and the padding through the arithmetic. They
 // can be fetched as 32-bit words, which is how this kernel reads them: half a warp takes one row,
@@ -136,47 +136,104 @@ __device__ __forceinline__ void add_quantised_row(float (&a)[8], float& bias_sum
     bias_sum = fmaf(__half2float(__ushort_as_half(static_cast<unsigned short>(hdr >> 16))), weight, bias_sum);
 }
 
+// Pools bags [bag0, bag0 + nb), nb <= 32, of one table (bag0 = t * B + b0) as one stream of lookups,
+// as pool_float_bags does for float rows: rounds of 2 * kSteps rows whatever the bags' lengths, the
+// next 32 ids requested before the current ones' rows, a bag closed (sum of the two half-warps, plus
+// the bias sum, stored) at the step that holds its last lookup.
 // kFull: D = 128, every lane of a half-warp has its code words (no lane sits out).
 template <typename OT, typename IndexT, bool kInt4, bool kWeighted, bool kFull>
-__device__ __forceinline__ void pool_quantised_bag(const NbitParams& p, const char* table, uint32_t row_stride,
-                                                   int D, int64_t num_rows, int64_t col, int64_t bag, int b,
-                                                   int lane) {
+__device__ __forceinline__ void pool_quantised_bags(const NbitParams& p, const char* table, uint32_t row_stride,
+                                                    int D, int64_t num_rows, int64_t col, int64_t bag0, int b0,
+                                                    int nb, int lane) {
   constexpr int kSteps = kInt4 ? 8 : 4;   // rows per half-warp whose words are in flight
-  const int64_t start = load_index<IndexT>(p.offsets, bag);
-  const int64_t end = load_index<IndexT>(p.offsets, bag + 1);
-  int len = end - start > 0x7fffffff ? 0x7fffffff : static_cast<int>(end - start);
-  const int pooled = len;                 // MEAN divides by the bag's length, skipped ids included
-  if (num_rows == 0) len = 0;             // a table without rows: every id is out of range
-  const IndexT* idx = reinterpret_cast<const IndexT*>(p.indices) + start;
-  const float* psw = kWeighted ? p.per_sample_weights + start : nullptr;
+  const int64_t begin = load_index<IndexT>(p.offsets, bag0);
+  int my_end = 0;
+  if (lane < nb) {
+    const int64_t e = load_index<IndexT>(p.offsets, bag0 + lane + 1) - begin;
+    my_end = e < 0 ? 0 : (e > 0x7fffffff ? 0x7fffffff : static_cast<int>(e));
+  }
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int below = __shfl_up_sync(kFullMask, my_end, o);
+    if (lane >= o && below > my_end) my_end = below;
+  }
+  const int total = __shfl_sync(kFullMask, my_end, nb - 1);
+  const IndexT* idx = reinterpret_cast<const IndexT*>(p.indices) + begin;
+  const float* psw = kWeighted ? p.per_sample_weights + begin : nullptr;
   const int half = lane >> 4, w = lane & 15;
   // this lane's code words: INT4 word w = elements 8w..8w+7; INT8 words w and w + 16 = elements
   // 4w..4w+3 and 64+4w..64+4w+3
   const bool on0 = kFull || (kInt4 ? 8 * w < D : 4 * w < D);
   const bool on1 = !kInt4 && (kFull || 64 + 4 * w < D);
   const char* lane_base = table + 4 + 4 * w;
+  const int64_t row_limit = num_rows >= 0 ? num_rows : int64_t{0xffffffff};
+  const bool mean = p.pooling_mode == B200TBE_POOL_MEAN;
+  const int rpd = static_cast<int>(p.rows_per_dest);
 
   float a[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) a[e] = 0.f;
   float bias_sum = 0.f;
+  int cur = 0;                                              // bag being summed (warp-uniform)
+  int cur_start = 0;
+  int cur_end = __shfl_sync(kFullMask, my_end, 0);
 
-  for (int c = 0; c < len; c += 32) {
-    const int n = len - c < 32 ? len - c : 32;
-    // this lane's row id; a skipped lookup (past the bag's end, id out of range) reads row 0 with
+  auto close_bag = [&]() {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) a[e] += __shfl_xor_sync(kFullMask, a[e], 16);
+    bias_sum += __shfl_xor_sync(kFullMask, bias_sum, 16);
+    if (half == 0) {
+      const int pooled = cur_end - cur_start;   // MEAN divides by the bag's length, skipped ids included
+      const float scale = (mean && pooled > 0) ? 1.f / static_cast<float>(pooled) : 1.f;
+      const int b = b0 + cur;
+      const int dest = b / rpd;
+      OT* dst = reinterpret_cast<OT* const*>(p.outputs)[dest] +
+                static_cast<int64_t>(b - dest * rpd) * p.output_stride + col;
+      float r[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) r[e] = (a[e] + bias_sum) * scale;
+      if (kInt4) {
+        // nibbles_to_half2 pairs nibble i with nibble i + 4: a[2i] = element 8w + i, a[2i + 1] = element 8w + 4 + i
+        const float e[8] = {r[0], r[2], r[4], r[6], r[1], r[3], r[5], r[7]};
+        if (on0) store_pooled<OT, 8>(dst + 8 * w, e);
+      } else {
+        if (on0) store_pooled<OT, 4>(dst + 4 * w, r);
+        if (on1) store_pooled<OT, 4>(dst + 64 + 4 * w, r + 4);
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) a[e] = 0.f;
+    bias_sum = 0.f;
+    ++cur;
+    cur_start = cur_end;
+    cur_end = __shfl_sync(kFullMask, my_end, cur & 31);
+  };
+
+  IndexT next_id = 0;
+  float next_w = 1.f;
+  if (lane < total) {
+    next_id = __ldg(idx + lane);
+    if (kWeighted) next_w = __ldg(psw + lane);
+  }
+  for (int c = 0; c < total; c += 32) {
+    const int n = total - c < 32 ? total - c : 32;
+    // this lane's row id; a skipped lookup (past the stream's end, id out of range) reads row 0 with
     // its header replaced by zero: scale 0 and bias 0 add nothing, and no load needs a test
     uint32_t my_row = 0;
     bool my_ok = false;
-    float my_w = 1.f;
+    const float my_w = next_w;
     if (lane < n) {
-      const int64_t i = static_cast<int64_t>(__ldg(idx + c + lane));
-      if (kWeighted) my_w = __ldg(psw + c + lane);
-      if (i < 0 || i >= (num_rows >= 0 ? num_rows : int64_t{0xffffffff})) {
+      const int64_t i = static_cast<int64_t>(next_id);
+      if (i < 0 || i >= row_limit) {
         if (p.status != nullptr) atomicOr(p.status, B200TBE_DEV_INDEX_OUT_OF_RANGE);
       } else {
         my_row = static_cast<uint32_t>(i);
         my_ok = true;
       }
+    }
+    if (c + 32 + lane < total) {
+      next_id = __ldg(idx + c + 32 + lane);
+      if (kWeighted) next_w = __ldg(psw + c + 32 + lane);
     }
     const uint32_t ok_mask = __ballot_sync(kFullMask, my_ok);
     for (int j = 0; j < n; j += 2 * kSteps) {
@@ -197,42 +254,37 @@ __device__ __forceinline__ void pool_quantised_bag(const NbitParams& p, const ch
         if (((ok_mask >> rr) & 1u) == 0 || j + 2 * u + half >= 32) hdr[u] = 0u;
       }
 #pragma unroll
-      for (int u = 0; u < kSteps; ++u)
-        add_quantised_row<kInt4, kWeighted>(a, bias_sum, hdr[u], w0[u], w1[u], wt[u]);
+      for (int u = 0; u < kSteps; ++u) {
+        const int step = c + j + 2 * u;           // lookups step and step + 1 of the stream
+        if (step + 2 < cur_end) {                 // both inside the open bag, which goes on
+          add_quantised_row<kInt4, kWeighted>(a, bias_sum, hdr[u], w0[u], w1[u], wt[u]);
+        } else if (j + 2 * u < n) {
+          // a bag ends in this step: each row goes to the bag that holds it, bags close in order
+          const int q = step + half;
+          bool pending = true;
+          while (cur < nb) {
+            if (pending && q < cur_end) {
+              add_quantised_row<kInt4, kWeighted>(a, bias_sum, hdr[u], w0[u], w1[u], wt[u]);
+              pending = false;
+            }
+            if (step + 2 < cur_end) break;
+            close_bag();
+          }
+        }
+      }
     }
   }
-#pragma unroll
-  for (int e = 0; e < 8; ++e) a[e] += __shfl_xor_sync(kFullMask, a[e], 16);
-  bias_sum += __shfl_xor_sync(kFullMask, bias_sum, 16);
-  if (half == 0) {
-    const float scale =
-        (p.pooling_mode == B200TBE_POOL_MEAN && pooled > 0) ? 1.f / static_cast<float>(pooled) : 1.f;
-    const int rpd = static_cast<int>(p.rows_per_dest);
-    const int dest = b / rpd;
-    OT* dst = reinterpret_cast<OT* const*>(p.outputs)[dest] +
-              static_cast<int64_t>(b - dest * rpd) * p.output_stride + col;
-    float r[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) r[e] = (a[e] + bias_sum) * scale;
-    if (kInt4) {
-      // nibbles_to_half2 pairs nibble i with nibble i + 4: a[2i] = element 8w + i, a[2i + 1] = element 8w + 4 + i
-      const float e[8] = {r[0], r[2], r[4], r[6], r[1], r[3], r[5], r[7]};
-      if (on0) store_pooled<OT, 8>(dst + 8 * w, e);
-    } else {
-      if (on0) store_pooled<OT, 4>(dst + 4 * w, r);
-      if (on1) store_pooled<OT, 4>(dst + 64 + 4 * w, r + 4);
-    }
-  }
+  while (cur < nb) close_bag();   // bags without lookups at the group's end (or a group without any)
 }
 
 template <typename OT, typename IndexT, bool kWeighted>
 __global__ void __launch_bounds__(kNbitBagThreads, kNbitBagCtasPerSm)
     tbe_nbit_bags_kernel(const __grid_constant__ NbitParams p) {
-  const int lane = threadIdx.x & 31;
-  const int64_t bag = static_cast<int64_t>(blockIdx.x) * kNbitBagWarps + (threadIdx.x >> 5);
-  if (bag >= static_cast<int64_t>(p.T) * p.B) return;
-  const int t = static_cast<int>(bag / p.B);
-  const int b = static_cast<int>(bag - static_cast<int64_t>(t) * p.B);
+  const int lane = threadIdx.x;
+  const int t = static_cast<int>(blockIdx.x / static_cast<unsigned>(p.groups_per_table));
+  const int b0 = static_cast<int>(blockIdx.x - static_cast<unsigned>(t) * p.groups_per_table) * p.bag_group;
+  const int nb = p.B - b0 < p.bag_group ? p.B - b0 : p.bag_group;
+  const int64_t bag0 = static_cast<int64_t>(t) * p.B + b0;
   const int ty = __ldg(p.weights_tys + t);
   const int D_begin = __ldg(p.D_offsets + t);
   const int D = __ldg(p.D_offsets + t + 1) - D_begin;
@@ -244,15 +296,15 @@ __global__ void __launch_bounds__(kNbitBagThreads, kNbitBagCtasPerSm)
   const uint32_t stride = static_cast<uint32_t>(row_stride);   // at most 4 + 128 bytes plus padding
   if (ty == B200TBE_INT4) {
     if (D == kNbitBagMaxD) {
-      pool_quantised_bag<OT, IndexT, true, kWeighted, true>(p, table, stride, D, num_rows, col, bag, b, lane);
+      pool_quantised_bags<OT, IndexT, true, kWeighted, true>(p, table, stride, D, num_rows, col, bag0, b0, nb, lane);
     } else {
-      pool_quantised_bag<OT, IndexT, true, kWeighted, false>(p, table, stride, D, num_rows, col, bag, b, lane);
+      pool_quantised_bags<OT, IndexT, true, kWeighted, false>(p, table, stride, D, num_rows, col, bag0, b0, nb, lane);
     }
   } else {
     if (D == kNbitBagMaxD) {
-      pool_quantised_bag<OT, IndexT, false, kWeighted, true>(p, table, stride, D, num_rows, col, bag, b, lane);
+      pool_quantised_bags<OT, IndexT, false, kWeighted, true>(p, table, stride, D, num_rows, col, bag0, b0, nb, lane);
     } else {
-      pool_quantised_bag<OT, IndexT, false, kWeighted, false>(p, table, stride, D, num_rows, col, bag, b, lane);
+      pool_quantised_bags<OT, IndexT, false, kWeighted, false>(p, table, stride, D, num_rows, col, bag0, b0, nb, lane);
     }
   }
 }
