@@ -33,8 +33,8 @@ L2_FLUSH_BYTES = 512 << 20
 # rows x D=128, B=65536, about 1.67 M lookups -- from the ncu capture summarised in
 # profiles/tbe_step_one_table_traffic.md. Tables are processed one after another, each with its own
 # rows, ids and gradient columns, so a step of T tables moves T times this.
-FWD_TRAFFIC_PER_TABLE = 109.9e6   # lookup kernel: 103.1 MB read + 6.8 MB written
-BWD_TRAFFIC_PER_TABLE = 256.2e6   # 20 kernels of one b200tbe_backward call: 213.4 MB read + 42.8 MB written
+FWD_TRAFFIC_PER_TABLE = 106.2e6   # lookup kernel: 101.5 MB read + 4.7 MB written
+BWD_TRAFFIC_PER_TABLE = 258.9e6   # 20 kernels of one b200tbe_backward call: 213.4 MB read + 45.5 MB written
 TRAFFIC_NOTE = ("one-table ncu capture x tables (profiles/tbe_step_one_table_traffic.md); bytes a kernel leaves "
                 "dirty in L2 when it ends are not in its DRAM write counter")
 TABLES_OVERRIDE = None   # --tables: fewer tables for --only runs (small profiler captures)
@@ -288,7 +288,7 @@ def reference_arm(args, cfg, rank, json_out):
 # The other named configurations, single GPU, one kernel (or kernel group) each
 # --------------------------------------------------------------------------------------------
 def bench_others(peak_gbs, iters=20, only=None):
-    """only: None (all), or one of 'jagged', 'fp32', 'train', 'nbit', 'nv12', 'permute'."""
+    """only: None (all), or one of 'jagged', 'fp32', 'train', 'uniform', 'nbit', 'nv12', 'permute'."""
     res = {}
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device="cuda")
     gen = torch.Generator(device="cuda").manual_seed(99)
@@ -329,6 +329,8 @@ def _others_tbe(res, entry, flush, gen, iters, only):
         _bench_fp32(entry, flush, gen, iters)
     if only in (None, "train"):
         _bench_train(entry, flush, gen, iters)
+    if only in (None, "uniform"):
+        _bench_uniform(entry, flush, gen, iters)
     if only in (None, "nbit"):
         _bench_nbit(entry, flush, gen, iters)
     if only in (None, "nv12"):
@@ -383,6 +385,39 @@ def _bench_train(entry, flush, gen, iters):
     ms, _ = time_launches(bwd, iters, flush)
     entry("tbe_fp16_backward_adagrad(config3)", workloads.backward_bytes(inp.num_lookups, U, D * 2, T, B, D, 4),
           ms, inp.num_lookups, {"kernels_per_call": backward_launches((E - 1).bit_length())})
+
+
+def _bench_uniform(entry, flush, gen, iters):
+    # The training kernels where no lookup repeats a row: 4 fp16 tables x 16 M rows x D=128 (16.4 GB),
+    # B=65536, every bag 32 uniform ids. Every row is a first touch, so the compulsory bytes ARE the
+    # traffic and the fraction of the HBM copy rate says how well the kernels gather from DRAM; the
+    # Zipf configurations above re-read most rows out of L2 and are bound by its row rate instead.
+    T, E, D, B, L = 4, 16_000_000, 128, 65536, 32
+    idx = torch.randint(0, E, (T * B * L,), device="cuda", generator=gen)
+    offs = torch.arange(T * B + 1, device="cuda", dtype=torch.int64) * L
+    U = sum(int(torch.unique(idx[t * B * L:(t + 1) * B * L]).numel()) for t in range(T))
+    n = T * B * L
+    W = uniform_half_table(T * E * D, -0.01, 0.01, gen)
+    mom = torch.zeros(T * E, device="cuda")
+    wo = torch.arange(T, device="cuda", dtype=torch.int64) * (E * D)
+    Do = torch.arange(T + 1, device="cuda", dtype=torch.int32) * D
+    hs = torch.arange(T + 1, device="cuda", dtype=torch.int64) * E
+    out = torch.empty((B, T * D), device="cuda", dtype=torch.float16)
+    grad = (torch.randn((B, T * D), device="cuda", generator=gen) * 0.1).half()
+    bits = (T * E - 1).bit_length()
+    scratch = torch.empty(cabi.backward_scratch_bytes(n, bits, D, T), dtype=torch.uint8, device="cuda")
+    fwd = lambda: cabi.forward(W, wo, Do, T * D, D, idx, offs, B, outputs=[out], output_stride=T * D,
+                               rows_per_dest=B, output_dtype=torch.float16)
+    bwd = lambda: cabi.backward(W, wo, Do, hs, bits, D, idx, offs, B, grad, cabi.OPT_ROWWISE_ADAGRAD, 0.01,
+                                1e-8, mom, hs[:-1], scratch=scratch, max_table_rows=E)
+    fwd(); bwd()
+    ms, _ = time_launches(fwd, max(5, iters // 2), flush)
+    entry("tbe_fp16_forward(uniform ids, 16 GB of rows)", workloads.forward_bytes(n, U, D * 2, T, B, D, 2), ms, n,
+          {"unique_rows": U})
+    ms, _ = time_launches(bwd, max(5, iters // 2), flush)
+    entry("tbe_fp16_backward_adagrad(uniform ids, 16 GB of rows)", workloads.backward_bytes(n, U, D * 2, T, B, D, 2),
+          ms, n, {"unique_rows": U, "kernels_per_call": backward_launches((E - 1).bit_length())})
+    del W, mom, idx, grad, scratch
 
 
 def _bench_permute(entry, flush, gen, iters):
@@ -643,7 +678,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-others", action="store_true", help="skip the single-kernel configurations")
     ap.add_argument("--small", action="store_true", help="tiny tables, for profiler captures and smoke runs")
-    ap.add_argument("--only", default=None, choices=["jagged", "fp32", "train", "nbit", "nv12", "permute", "step"],
+    ap.add_argument("--only", default=None, choices=["jagged", "fp32", "train", "uniform", "nbit", "nv12", "permute", "step"],
                     help="run one single-GPU configuration alone (few launches; for profiler captures); "
                          "'step' is the bench step itself cut to --tables tables (default 2)")
     ap.add_argument("--iters", type=int, default=20, help="timed launches per single-GPU configuration")
