@@ -33,6 +33,13 @@ inline int bag_group_for(int64_t bags) {
   return per_slot < 1 ? 1 : (per_slot > 32 ? 32 : static_cast<int>(per_slot));
 }
 
+// base + row * row_bytes as one multiply-add (the compiler otherwise spends a multiply and two 64-bit adds).
+__device__ __forceinline__ const char* row_address(const char* base, uint32_t row, uint32_t row_bytes) {
+  const char* p;
+  asm("mad.wide.u32 %0, %1, %2, %3;" : "=l"(p) : "r"(row), "r"(row_bytes), "l"(base));
+  return p;
+}
+
 __device__ __forceinline__ uint4 ldg_cached16(const void* p) {
   uint4 v;
   asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -162,7 +169,7 @@ __device__ __forceinline__ void pool_float_bag(const BagLaunch<OT>& p, const cha
         const int rr = j + u * G + h;
         const uint32_t row = __shfl_sync(kFullMask, my_row, rr);
         if (kWeighted) w[u] = __shfl_sync(kFullMask, my_w, rr);
-        x[u] = ldg_cached16(lane_any + static_cast<uint64_t>(row) * static_cast<uint32_t>(row_bytes));
+        x[u] = ldg_cached16(row_address(lane_any, row, static_cast<uint32_t>(row_bytes)));
       }
 #pragma unroll
       for (int u = 0; u < kLoads; ++u) {
@@ -183,7 +190,7 @@ __device__ __forceinline__ void pool_float_bag(const BagLaunch<OT>& p, const cha
         if (kWeighted) w[u] = __shfl_sync(kFullMask, my_w, rr & 31);
         x[u] = make_uint4(0u, 0u, 0u, 0u);  // +0.0 in either type: adding it changes nothing
         if (rr < n && row != kNoRow && active)
-          x[u] = ldg_cached16(lane_base + static_cast<uint64_t>(row) * static_cast<uint32_t>(row_bytes));
+          x[u] = ldg_cached16(row_address(lane_base, row, static_cast<uint32_t>(row_bytes)));
       }
 #pragma unroll
       for (int u = 0; u < kLoads; ++u) {
@@ -324,7 +331,7 @@ __device__ __forceinline__ void pool_float_bags(const BagLaunch<OT>& p, const ch
           const int rr = j + u * G + h;
           const uint32_t row = __shfl_sync(kFullMask, my_row, rr);
           if (kWeighted) w[u] = __shfl_sync(kFullMask, my_w, rr);
-          x[u] = ldg_cached16(lane_any + static_cast<uint64_t>(row) * static_cast<uint32_t>(row_bytes));
+          x[u] = ldg_cached16(row_address(lane_any, row, static_cast<uint32_t>(row_bytes)));
         }
       } else {
 #pragma unroll
@@ -334,8 +341,19 @@ __device__ __forceinline__ void pool_float_bags(const BagLaunch<OT>& p, const ch
           if (kWeighted) w[u] = __shfl_sync(kFullMask, my_w, rr & 31);
           x[u] = make_uint4(0u, 0u, 0u, 0u);  // +0.0 in either type: adding it changes nothing
           if (rr < n && row != kNoRow && active)
-            x[u] = ldg_cached16(lane_base + static_cast<uint64_t>(row) * static_cast<uint32_t>(row_bytes));
+            x[u] = ldg_cached16(row_address(lane_base, row, static_cast<uint32_t>(row_bytes)));
         }
+      }
+      if (c + j + round_rows < cur_end) {        // the whole round inside the open bag, which goes on
+#pragma unroll
+        for (int u = 0; u < kLoads; ++u) {
+          if (kWeighted) {
+            Vec16<WT>::fma(acc, x[u], w[u]);
+          } else {
+            Vec16<WT>::add(acc, x[u]);
+          }
+        }
+        continue;
       }
 #pragma unroll
       for (int u = 0; u < kLoads; ++u) {
