@@ -245,13 +245,19 @@ __device__ __forceinline__ void pool_quantised_bags(const NbitParams& p, const c
         const uint32_t row = __shfl_sync(kFullMask, my_row, rr);
         wt[u] = 1.f;
         if (kWeighted) wt[u] = __shfl_sync(kFullMask, my_w, rr);
-        const char* src = lane_base + static_cast<uint64_t>(row) * row_stride;
+        const char* src = row_address(lane_base, row, row_stride);
         hdr[u] = ldg_cached4(src - 4 - 4 * w);
         w0[u] = 0u;
         w1[u] = 0u;
         if (on0) w0[u] = ldg_cached4(src);
         if (on1) w1[u] = ldg_cached4(src + 64);
         if (((ok_mask >> rr) & 1u) == 0 || j + 2 * u + half >= 32) hdr[u] = 0u;
+      }
+      if (c + j + 2 * kSteps < cur_end) {         // the whole round inside the open bag, which goes on
+#pragma unroll
+        for (int u = 0; u < kSteps; ++u)
+          add_quantised_row<kInt4, kWeighted>(a, bias_sum, hdr[u], w0[u], w1[u], wt[u]);
+        continue;
       }
 #pragma unroll
       for (int u = 0; u < kSteps; ++u) {
