@@ -839,7 +839,7 @@ def main():
         "traffic_note": TRAFFIC_NOTE, "peak_kind": "of " + peak_kind, "algorithmic_bytes": bwd_bytes,
     }
     line["roofline_forward"] = {
-        "bound": "hbm", "kernel": "tbe_forward_bags_kernel", "achieved": fwd_bytes / fwd_avg / 1e6,
+        "bound": "hbm", "kernel": "tbe_forward_bag_groups_kernel", "achieved": fwd_bytes / fwd_avg / 1e6,
         "peak": peak_gbs, "unit": "GB/s", "frac": fwd_bytes / fwd_avg / 1e6 / peak_gbs,
         "traffic": None if FWD_TRAFFIC_PER_TABLE is None else FWD_TRAFFIC_PER_TABLE * step.T,
         "traffic_note": TRAFFIC_NOTE, "peak_kind": "of " + peak_kind, "algorithmic_bytes": fwd_bytes,

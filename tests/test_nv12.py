@@ -59,6 +59,31 @@ def test_whole_frames_equal_the_references_kernel(fullrange):
     assert np.array_equal(got, want)
 
 
+def _golden():
+    import os
+    return np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "nv12_reference.npz"))
+
+
+def test_committed_vectors_of_the_references_kernel():
+    """tests/golden/nv12_reference.npz holds what the reference's kernel (compiled for the host, see
+    tests/golden/make_nv12_golden.py) returned for two Tile-Y frames, a surface's tile offsets and
+    4096 YUV triples; the restatement reproduces all of it without the reference tree."""
+    g = _golden()
+    for name in ("a", "b"):
+        w, h, stride = (int(v) for v in g[f"{name}_shape"])
+        for key, fullrange in (("limited", False), ("full", True)):
+            got = oracle.nv12_to_rgb(g[f"{name}_y"], g[f"{name}_uv"], w, h, stride, fullrange, tiled=True)
+            assert np.array_equal(got, g[f"{name}_rgb_{key}"]), (name, key)
+    offs = g["tile_offsets_256x64"]
+    for y in range(offs.shape[0]):
+        for x in range(offs.shape[1]):
+            assert oracle.nv12_offset(x, y, 256, True) == int(offs[y, x])
+    for key, fullrange in (("limited", False), ("full", True)):
+        want = g[f"triples_rgb_{key}"]
+        for (yy, u, v), rgb in zip(g["triples"][:512], want[:512]):
+            assert oracle.nv12_pixel(int(yy), int(u), int(v), fullrange) == tuple(int(c) for c in rgb)
+
+
 @pytest.mark.parametrize("yuv,rgb", [
     ((16, 128, 128), (0, 0, 0)),          # black
     ((235, 128, 128), (255, 255, 255)),   # white

@@ -38,6 +38,30 @@ def test_matches_oracle_bit_for_bit(width, height, stride, tiled, fullrange):
     assert np.array_equal(got, want)
 
 
+def test_committed_vectors_of_the_references_kernel():
+    """The CUDA kernel against what the reference's own kernel returned (tests/golden/nv12_reference.npz,
+    made by tests/golden/make_nv12_golden.py from the reference's source compiled for the host): two
+    Tile-Y frames in both ranges, and 4096 YUV triples laid out as a one-row linear surface."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "nv12_reference.npz"))
+    for name in ("a", "b"):
+        w, h, stride = (int(v) for v in g[f"{name}_shape"])
+        for key, fullrange in (("limited", False), ("full", True)):
+            got = cabi.nv12_to_rgb(torch.from_numpy(g[f"{name}_y"]).cuda(), torch.from_numpy(g[f"{name}_uv"]).cuda(),
+                                   w, h, stride, fullrange, True).cpu().numpy()
+            assert np.array_equal(got, g[f"{name}_rgb_{key}"]), (name, key)
+    # triples: pixel pairs (2 i, 2 i + 1) of one row share chroma pair i, so give both the same luma
+    t = g["triples"]
+    n = t.shape[0]
+    y = np.repeat(t[:, 0], 2)[None, :].copy()
+    uv = t[:, 1:3].reshape(1, 2 * n).copy()
+    for key, fullrange in (("limited", False), ("full", True)):
+        got = cabi.nv12_to_rgb(torch.from_numpy(y).cuda(), torch.from_numpy(uv).cuda(), 2 * n, 1, 2 * n,
+                               fullrange, False).cpu().numpy()
+        assert np.array_equal(got[0, 0::2], g[f"triples_rgb_{key}"])
+        assert np.array_equal(got[0, 1::2], g[f"triples_rgb_{key}"])
+
+
 def test_every_yuv_triple_of_a_sweep_matches():
     """All 256 luma values against a grid of chroma pairs: the float path has no off-by-one."""
     width, height, stride = 256, 64, 256
