@@ -81,12 +81,19 @@ __global__ void __launch_bounds__(kSortThreads)
   __shared__ uint32_t hist[kMaxRadix];
   const TilePlace tp = place_tile<kTile>(n, radix, num_tiles, desc, seg_tile_base, total_tiles);
   if (!tp.live) return;
+  // all of the thread's keys are requested before the first is counted
+  KeyT k[kItems];
+#pragma unroll
+  for (int i = 0; i < kItems; ++i) {
+    const int it = i * kSortThreads + threadIdx.x;
+    k[i] = it < tp.tile_n ? keys[tp.base + it] : KeyT(0);
+  }
   for (int d = threadIdx.x; d < radix; d += kSortThreads) hist[d] = 0;
   __syncthreads();
 #pragma unroll
   for (int i = 0; i < kItems; ++i) {
     const int it = i * kSortThreads + threadIdx.x;
-    if (it < tp.tile_n) atomicAdd(&hist[static_cast<uint32_t>(keys[tp.base + it] >> shift) & mask], 1u);
+    if (it < tp.tile_n) atomicAdd(&hist[static_cast<uint32_t>(k[i] >> shift) & mask], 1u);
   }
   __syncthreads();
   for (int d = threadIdx.x; d < radix; d += kSortThreads) counts[d * tp.stride + tp.col] = hist[d];
