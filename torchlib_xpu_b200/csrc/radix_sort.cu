@@ -115,23 +115,18 @@ struct ScatterSmem {
   uint32_t vals[SortTile<KeyT>::kTile];
 };
 
-// kRadix: capacity of the digit tables (>= radix, a multiple of kSortThreads).
-template <typename KeyT, int kRadix>
-__global__ void __launch_bounds__(kSortThreads, kRadix > 1024 ? 3 : 4)
-    sort_scatter_kernel(const KeyT* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
-                        KeyT* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int64_t n,
-                        int shift, uint32_t mask, int radix, int digit_bits,
-                        const uint32_t* __restrict__ positions, int num_tiles,
-                        const uint4* __restrict__ desc, const uint32_t* __restrict__ seg_tile_base,
-                        const uint32_t* __restrict__ total_tiles) {
+// kRadix: capacity of the digit tables (>= radix, a multiple of kSortThreads). kFull: the tile holds
+// kTile keys (every tile but a segment's last), so no step tests a position against the tile's end.
+template <typename KeyT, int kRadix, bool kFull>
+__device__ __forceinline__ void scatter_tile(ScatterSmem<KeyT, kRadix>& sm, const TilePlace& tp,
+                                             const KeyT* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
+                                             KeyT* __restrict__ keys_out, uint32_t* __restrict__ vals_out,
+                                             int shift, uint32_t mask, int radix,
+                                             const uint32_t* __restrict__ positions) {
   constexpr int kItems = SortTile<KeyT>::kItems;
   constexpr int kTile = SortTile<KeyT>::kTile;
   constexpr int kDigitsPerThread = kRadix / kSortThreads;
-  extern __shared__ __align__(16) unsigned char sort_smem[];
-  ScatterSmem<KeyT, kRadix>& sm = *reinterpret_cast<ScatterSmem<KeyT, kRadix>*>(sort_smem);
-
-  const TilePlace tp = place_tile<kTile>(n, radix, num_tiles, desc, seg_tile_base, total_tiles);
-  if (!tp.live) return;
+  constexpr int kBits = kRadix == 256 ? 8 : (kRadix == 1024 ? 10 : 11);   // bits above the pass's digit are zero
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   {
     uint32_t* z = reinterpret_cast<uint32_t*>(&sm.warp_hist[0][0]);
@@ -139,7 +134,7 @@ __global__ void __launch_bounds__(kSortThreads, kRadix > 1024 ? 3 : 4)
   }
 
   const int64_t base = tp.base;
-  const int tile_n = tp.tile_n;
+  const int tile_n = kFull ? kTile : tp.tile_n;
   const int warp_base = warp * (kItems * 32);
   const uint32_t lanemask_lt = (1u << lane) - 1u;
 
@@ -148,7 +143,7 @@ __global__ void __launch_bounds__(kSortThreads, kRadix > 1024 ? 3 : 4)
 #pragma unroll
   for (int r = 0; r < kItems; ++r) {
     const int it = warp_base + r * 32 + lane;
-    k[r] = it < tile_n ? keys_in[base + it] : KeyT(0);
+    k[r] = (kFull || it < tile_n) ? keys_in[base + it] : KeyT(0);
   }
   __syncthreads();
 
@@ -156,12 +151,13 @@ __global__ void __launch_bounds__(kSortThreads, kRadix > 1024 ? 3 : 4)
 #pragma unroll
   for (int r = 0; r < kItems; ++r) {
     const int it = warp_base + r * 32 + lane;
-    const bool valid = it < tile_n;
+    const bool valid = kFull || it < tile_n;
     rank[r] = 0;
     const uint32_t d = static_cast<uint32_t>(k[r] >> shift) & mask;
     // lanes holding the same digit, found one bit at a time with warp votes
-    uint32_t peers = __ballot_sync(kFullMask, valid);
-    for (int b = 0; b < digit_bits; ++b) {
+    uint32_t peers = kFull ? kFullMask : __ballot_sync(kFullMask, valid);
+#pragma unroll
+    for (int b = 0; b < kBits; ++b) {
       const bool bit = (d >> b) & 1u;
       const uint32_t with_bit = __ballot_sync(kFullMask, bit);
       peers &= bit ? with_bit : ~with_bit;
@@ -212,7 +208,7 @@ __global__ void __launch_bounds__(kSortThreads, kRadix > 1024 ? 3 : 4)
 #pragma unroll
   for (int r = 0; r < kItems; ++r) {
     const int it = warp_base + r * 32 + lane;
-    if (it < tile_n) {
+    if (kFull || it < tile_n) {
       const uint32_t d = static_cast<uint32_t>(k[r] >> shift) & mask;
       const uint32_t pos = sm.digit_start[d] + sm.warp_hist[warp][d] + rank[r];
       sm.keys[pos] = k[r];
@@ -224,12 +220,43 @@ __global__ void __launch_bounds__(kSortThreads, kRadix > 1024 ? 3 : 4)
   for (int j = 0; j < kDigitsPerThread; ++j) sm.delta[threadIdx.x * kDigitsPerThread + j] = totals[j];
   __syncthreads();
 
-  for (int i = threadIdx.x; i < tile_n; i += kSortThreads) {
-    const KeyT key = sm.keys[i];
-    const uint32_t d = static_cast<uint32_t>(key >> shift) & mask;
-    const uint32_t dst = static_cast<uint32_t>(i) + sm.delta[d];
-    keys_out[dst] = key;
-    vals_out[dst] = sm.vals[i];
+  if (kFull) {
+#pragma unroll 4
+    for (int i = threadIdx.x; i < kTile; i += kSortThreads) {
+      const KeyT key = sm.keys[i];
+      const uint32_t d = static_cast<uint32_t>(key >> shift) & mask;
+      const uint32_t dst = static_cast<uint32_t>(i) + sm.delta[d];
+      keys_out[dst] = key;
+      vals_out[dst] = sm.vals[i];
+    }
+  } else {
+    for (int i = threadIdx.x; i < tile_n; i += kSortThreads) {
+      const KeyT key = sm.keys[i];
+      const uint32_t d = static_cast<uint32_t>(key >> shift) & mask;
+      const uint32_t dst = static_cast<uint32_t>(i) + sm.delta[d];
+      keys_out[dst] = key;
+      vals_out[dst] = sm.vals[i];
+    }
+  }
+}
+
+template <typename KeyT, int kRadix>
+__global__ void __launch_bounds__(kSortThreads, kRadix > 1024 ? 3 : 4)
+    sort_scatter_kernel(const KeyT* __restrict__ keys_in, const uint32_t* __restrict__ vals_in,
+                        KeyT* __restrict__ keys_out, uint32_t* __restrict__ vals_out, int64_t n,
+                        int shift, uint32_t mask, int radix,
+                        const uint32_t* __restrict__ positions, int num_tiles,
+                        const uint4* __restrict__ desc, const uint32_t* __restrict__ seg_tile_base,
+                        const uint32_t* __restrict__ total_tiles) {
+  constexpr int kTile = SortTile<KeyT>::kTile;
+  extern __shared__ __align__(16) unsigned char sort_smem[];
+  ScatterSmem<KeyT, kRadix>& sm = *reinterpret_cast<ScatterSmem<KeyT, kRadix>*>(sort_smem);
+  const TilePlace tp = place_tile<kTile>(n, radix, num_tiles, desc, seg_tile_base, total_tiles);
+  if (!tp.live) return;
+  if (tp.tile_n == kTile) {
+    scatter_tile<KeyT, kRadix, true>(sm, tp, keys_in, vals_in, keys_out, vals_out, shift, mask, radix, positions);
+  } else {
+    scatter_tile<KeyT, kRadix, false>(sm, tp, keys_in, vals_in, keys_out, vals_out, shift, mask, radix, positions);
   }
 }
 
@@ -318,7 +345,7 @@ int launch_scatter(const KeyT* kin, const uint32_t* vin, KeyT* kout, uint32_t* v
     return B200TBE_ERR_LAUNCH;
   const int radix = 1 << a.bits;
   kernel<<<a.tiles, kSortThreads, smem, stream>>>(
-      kin, vin, kout, vout, a.n, a.shift, static_cast<uint32_t>(radix - 1), radix, a.bits, a.counts,
+      kin, vin, kout, vout, a.n, a.shift, static_cast<uint32_t>(radix - 1), radix, a.counts,
       a.tiles, a.plan ? a.plan->tile_desc : nullptr, a.plan ? a.plan->seg_tile_base : nullptr,
       a.plan ? a.plan->total_tiles : nullptr);
   return B200TBE_OK;
