@@ -233,7 +233,7 @@ class ShardedTbeStep:
 # --------------------------------------------------------------------------------------------
 # CPU arm: FBGEMM-core forward + the C oracle's backward on a bounded sample of the same workload
 # --------------------------------------------------------------------------------------------
-def cpu_sample_rate(cfg, budget_s=12.0):
+def cpu_sample_rate(cfg, limit_s=12.0):
     """One table of the bench step at the full batch (so that the share of repeated rows is the
     step's own), forward by FBGEMM-core + backward/Adagrad by the C oracle, on every core this
     process may run on -- set explicitly: launchers export OMP_NUM_THREADS=1."""
@@ -256,7 +256,7 @@ def cpu_sample_rate(cfg, budget_s=12.0):
         oracle.tbe_backward(W, oracle.FP16, wo, Do, hs, B, inp.indices, inp.offsets, grad, mom, hs[:-1],
                             oracle.ROWWISE_ADAGRAD, 0.01, 1e-8)
         reps += 1
-        if time.perf_counter() - t0 > budget_s or reps >= 400:
+        if time.perf_counter() - t0 > limit_s or reps >= 400:
             break
     dt = time.perf_counter() - t0
     sample = ("%d reps of fwd (FBGEMM-core EmbeddingSpMDM, torch-bundled) + bwd/Adagrad (C oracle) on "
@@ -269,8 +269,8 @@ def reference_arm(args, cfg, rank, json_out):
     if rank != 0:
         return
     steps, warm = args.steps, args.warmup
-    per_step_budget = max(0.5, min(8.0, 100.0 / max(1, steps + warm)))
-    rate, threads, sample, sec = cpu_sample_rate(cfg, budget_s=per_step_budget * (steps + warm))
+    per_step_limit = max(0.5, min(8.0, 100.0 / max(1, steps + warm)))
+    rate, threads, sample, sec = cpu_sample_rate(cfg, limit_s=per_step_limit * (steps + warm))
     line = {
         "impl": "reference", "metric": "TBE pooled-row lookups/s (fwd + bwd with fused row-wise Adagrad)",
         "value": rate, "unit": "lookups/s", "n_gpus": args.gpus, "steps": steps, "warmup": warm,

@@ -112,3 +112,49 @@ def test_nbit_register_gather_shapes(ty, D, weighted):
     got, status = _run(W, wo, tys_a, Do, rows, B, indices, offsets, psw, oracle.MEAN, torch.float32, 16)
     assert status == 0
     np.testing.assert_allclose(got.cpu().numpy(), want, rtol=1e-5, atol=1e-5)
+
+
+@pytest.mark.parametrize("weighted,pooling,idx_dtype,B", [
+    (False, oracle.SUM, np.int64, 16001),      # groups of 3 bags, the last group short
+    (True, oracle.MEAN, np.int32, 40000),      # groups of 8 (the most a warp takes)
+    (False, oracle.MEAN, np.int32, 25013),
+])
+def test_nbit_groups_of_bags(weighted, pooling, idx_dtype, B):
+    """A grid of more than about 47 k bags gives every warp a GROUP of consecutive bags to pool as one
+    stream of lookups. INT8 and INT4 rows of 128, 64 and 20 / 40 elements (and a table of a type the
+    register kernel leaves to the ring engine), bags of 0 to 40 lookups, runs of empty bags -- the tail
+    of a table and whole groups included -- and ids out of range."""
+    rng = workloads.rng_for(320 + B)
+    tys = [oracle.INT8, oracle.INT4, oracle.INT8, oracle.INT4, oracle.INT2, oracle.INT8]
+    Ds = [128, 128, 64, 40, 64, 20]
+    rows = [3000, 2000, 1000, 500, 300, 600]
+    T = len(Ds)
+    W, wo, Do, tys_a = helpers.quantised_tables(rng, rows, Ds, tys, 16)
+    lengths, _, _ = helpers.ragged_bags(rng, T, B, rows, 0, 40, empty_fraction=0.33)
+    lengths[B - 40:B] = 0
+    lengths[2 * B:2 * B + 64] = 0
+    lengths[-5:] = 0
+    offsets = np.zeros(T * B + 1, dtype=np.int64)
+    np.cumsum(lengths, out=offsets[1:])
+    indices = np.zeros(int(offsets[-1]), dtype=np.int64)
+    for t in range(T):
+        a, b = int(offsets[t * B]), int(offsets[(t + 1) * B])
+        indices[a:b] = rng.integers(0, rows[t], size=b - a, dtype=np.int64)
+    bad_at = rng.choice(indices.size, size=200, replace=False)
+    bad = indices.copy()
+    bad[bad_at[:100]] = 5000               # past every table
+    bad[bad_at[100:]] = -1
+    psw = rng.random(indices.size).astype(np.float32) if weighted else None
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = cabi.nbit_forward(_dev(W), _dev(wo), _dev(tys_a), _dev(Do), int(Do[-1]), int(np.max(np.diff(Do))),
+                            _dev(bad.astype(idx_dtype)), _dev(offsets.astype(idx_dtype)), B, pooling,
+                            None if psw is None else _dev(psw), torch.float32, 16,
+                            _dev(np.asarray(rows, dtype=np.int64)), status)
+    torch.cuda.synchronize()
+    assert int(status.item()) & cabi.DEV_INDEX_OUT_OF_RANGE
+    # flagged lookups contribute nothing (MEAN still divides by the bag's length)
+    keep = np.ones(indices.size, dtype=np.float32)
+    keep[bad_at] = 0.0
+    want = oracle.nbit_forward(W, wo, tys_a, Do, 16, B, np.where(keep > 0, indices, 0), offsets,
+                               keep if psw is None else psw * keep, pooling)
+    np.testing.assert_allclose(got.cpu().numpy(), want, rtol=RTOL, atol=ATOL)
