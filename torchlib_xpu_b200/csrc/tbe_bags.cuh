@@ -270,29 +270,47 @@ __device__ __forceinline__ void pool_float_bags(const BagLaunch<OT>& p, const ch
   int cur_start = 0;
   int cur_end = __shfl_sync(kFullMask, my_end, 0);
 
+  // where bag `cur` goes: consecutive bags are consecutive rows of a destination
+  int dest = b0 / rpd;
+  int row_in_dest = b0 - dest * rpd;
+  OT* dst = p.outputs[dest] + static_cast<int64_t>(row_in_dest) * p.output_stride + col + v * kE;
+
   // closes bag `cur`: its sum is spread over the row groups
   auto close_bag = [&]() {
-    for (int o = gs; o < 32; o <<= 1) {
+    const int len = cur_end - cur_start;
+    const float scale = (mean && len > 0) ? 1.f / static_cast<float>(len) : 1.f;
+    if (kE == 8 && gs == 16) {
+      // two groups: each keeps half of the lane's elements, so one exchange of four values does it
+      float r[4];
 #pragma unroll
-      for (int e = 0; e < kE; ++e) acc[e] += __shfl_xor_sync(kFullMask, acc[e], o);
-    }
-    if (h == 0 && active) {
-      const int len = cur_end - cur_start;
-      const float scale = (mean && len > 0) ? 1.f / static_cast<float>(len) : 1.f;
-      const int b = b0 + cur;
-      const int dest = b / rpd;
-      OT* dst = p.outputs[dest] + static_cast<int64_t>(b - dest * rpd) * p.output_stride + col + v * kE;
-      float r[kE];
+      for (int e = 0; e < 4; ++e) {
+        const float other = __shfl_xor_sync(kFullMask, h ? acc[e] : acc[e + 4], 16);
+        r[e] = ((h ? acc[e + 4] : acc[e]) + other) * scale;
+      }
+      if (active) store_pooled<OT, 4>(dst + 4 * h, r);
+    } else {
+      for (int o = gs; o < 32; o <<= 1) {
 #pragma unroll
-      for (int e = 0; e < kE; ++e) r[e] = acc[e] * scale;
+        for (int e = 0; e < kE; ++e) acc[e] += __shfl_xor_sync(kFullMask, acc[e], o);
+      }
+      if (h == 0 && active) {
+        float r[kE];
 #pragma unroll
-      for (int e = 0; e < kE; e += 4) store_pooled<OT, 4>(dst + e, r + e);
+        for (int e = 0; e < kE; ++e) r[e] = acc[e] * scale;
+#pragma unroll
+        for (int e = 0; e < kE; e += 4) store_pooled<OT, 4>(dst + e, r + e);
+      }
     }
 #pragma unroll
     for (int e = 0; e < kE; ++e) acc[e] = 0.f;
     ++cur;
     cur_start = cur_end;
     cur_end = __shfl_sync(kFullMask, my_end, cur & 31);
+    dst += p.output_stride;
+    if (++row_in_dest == rpd && cur < nb) {
+      row_in_dest = 0;
+      dst = p.outputs[++dest] + col + v * kE;
+    }
   };
 
   IndexT next_id = 0;
