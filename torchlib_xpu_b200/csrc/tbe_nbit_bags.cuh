@@ -178,28 +178,30 @@ __device__ __forceinline__ void pool_quantised_bags(const NbitParams& p, const c
   int cur_start = 0;
   int cur_end = __shfl_sync(kFullMask, my_end, 0);
 
+  // where bag `cur` goes: consecutive bags are consecutive rows of a destination
+  int dest = b0 / rpd;
+  int row_in_dest = b0 - dest * rpd;
+  OT* dst = reinterpret_cast<OT* const*>(p.outputs)[dest] + static_cast<int64_t>(row_in_dest) * p.output_stride + col;
+
+  // closes bag `cur`: each half-warp keeps half of its lanes' sums (INT8: half 0 the first code word's
+  // elements, half 1 the second's; INT4: the word's low and high four elements), so one exchange of
+  // four values and the bias sum does it
   auto close_bag = [&]() {
-#pragma unroll
-    for (int e = 0; e < 8; ++e) a[e] += __shfl_xor_sync(kFullMask, a[e], 16);
+    const int pooled = cur_end - cur_start;   // MEAN divides by the bag's length, skipped ids included
+    const float scale = (mean && pooled > 0) ? 1.f / static_cast<float>(pooled) : 1.f;
     bias_sum += __shfl_xor_sync(kFullMask, bias_sum, 16);
-    if (half == 0) {
-      const int pooled = cur_end - cur_start;   // MEAN divides by the bag's length, skipped ids included
-      const float scale = (mean && pooled > 0) ? 1.f / static_cast<float>(pooled) : 1.f;
-      const int b = b0 + cur;
-      const int dest = b / rpd;
-      OT* dst = reinterpret_cast<OT* const*>(p.outputs)[dest] +
-                static_cast<int64_t>(b - dest * rpd) * p.output_stride + col;
-      float r[8];
+    float r[4];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) r[e] = (a[e] + bias_sum) * scale;
-      if (kInt4) {
-        // nibbles_to_half2 pairs nibble i with nibble i + 4: a[2i] = element 8w + i, a[2i + 1] = element 8w + 4 + i
-        const float e[8] = {r[0], r[2], r[4], r[6], r[1], r[3], r[5], r[7]};
-        if (on0) store_pooled<OT, 8>(dst + 8 * w, e);
-      } else {
-        if (on0) store_pooled<OT, 4>(dst + 4 * w, r);
-        if (on1) store_pooled<OT, 4>(dst + 64 + 4 * w, r + 4);
-      }
+    for (int e = 0; e < 4; ++e) {
+      // nibbles_to_half2 pairs nibble i with nibble i + 4: a[2i] = element 8w + i, a[2i + 1] = element 8w + 4 + i
+      const int keep0 = kInt4 ? 2 * e : e, keep1 = kInt4 ? 2 * e + 1 : e + 4;
+      const float other = __shfl_xor_sync(kFullMask, half ? a[keep0] : a[keep1], 16);
+      r[e] = ((half ? a[keep1] : a[keep0]) + other + bias_sum) * scale;
+    }
+    if (kInt4) {
+      if (on0) store_pooled<OT, 4>(dst + 8 * w + 4 * half, r);
+    } else {
+      if (half ? on1 : on0) store_pooled<OT, 4>(dst + 64 * half + 4 * w, r);
     }
 #pragma unroll
     for (int e = 0; e < 8; ++e) a[e] = 0.f;
@@ -207,6 +209,11 @@ __device__ __forceinline__ void pool_quantised_bags(const NbitParams& p, const c
     ++cur;
     cur_start = cur_end;
     cur_end = __shfl_sync(kFullMask, my_end, cur & 31);
+    dst += p.output_stride;
+    if (++row_in_dest == rpd && cur < nb) {
+      row_in_dest = 0;
+      dst = reinterpret_cast<OT* const*>(p.outputs)[++dest] + col;
+    }
   };
 
   IndexT next_id = 0;
