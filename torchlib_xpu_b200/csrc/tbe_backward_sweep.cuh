@@ -42,16 +42,19 @@ __host__ __device__ constexpr int sweep_loads() {
   return kC <= 2 ? 4 : 2;
 }
 // one fp16 quad per lane of gradient and of weights costs two registers each per position: eight
-// positions in flight; anything wider, four (or two)
-template <typename WT, typename GT, bool kScaled, int kC>
+// positions in flight where the whole warp sweeps one span; anything wider, or several spans per
+// warp (which also keep the one-lookup runs' pass in registers), four (or two)
+template <typename WT, typename GT, bool kScaled, int kC, int GS = 32>
 __host__ __device__ constexpr int sweep_loads_for() {
-  return kC == 1 && sizeof(GT) == 2 && sizeof(WT) == 2 && !kScaled ? 8 : sweep_loads<kC>();
+  return kC == 1 && GS == 32 && sizeof(GT) == 2 && sizeof(WT) == 2 && !kScaled ? 8 : sweep_loads<kC>();
 }
 template <typename WT, typename GT, int kC>
 __host__ __device__ constexpr int sweep_ctas_per_sm() {
-  // CTAs (= warps) per SM; the register file allows 65536 / (32 * this) registers per thread
-  return kC > 2 ? 16 : (kC == 2 ? (sizeof(WT) == 2 && sizeof(GT) == 2 ? 20 : 16)
-                                : (sizeof(WT) == 2 && sizeof(GT) == 2 ? 32 : 24));
+  // CTAs (= warps) per SM; the register file allows 65536 / (32 * this) registers per thread. One quad
+  // per lane of fp16 weights fits 64 registers with either gradient type (26 tables x 1 M rows with
+  // fp32 gradients: 0.762 ms at 32 CTAs, 0.785 at 24, 0.790 at 28; eight positions in flight at 20 or
+  // 16 CTAs: 0.815, 0.854)
+  return kC > 2 ? 16 : (kC == 2 ? (sizeof(WT) == 2 && sizeof(GT) == 2 ? 20 : 16) : (sizeof(WT) == 2 ? 32 : 24));
 }
 constexpr uint32_t kNoSlice = 0xffffffffu;
 constexpr uint32_t kSpanTailOwner = 1u;   // the span's last run continues to the right; its piece is in the tail slot
@@ -545,7 +548,7 @@ __device__ __forceinline__ void sweep_span(const BwdDev& p, const SpanCtx& sc, c
   }
 }
 
-template <typename WT, typename GT, bool kScaled, int GS, int kC, int kMinCtas, int kLoads = sweep_loads_for<WT, GT, kScaled, kC>()>
+template <typename WT, typename GT, bool kScaled, int GS, int kC, int kMinCtas, int kLoads = sweep_loads_for<WT, GT, kScaled, kC, GS>()>
 __global__ void __launch_bounds__(kSweepThreads, kMinCtas)
     sweep_runs_kernel(const __grid_constant__ BwdDev p) {
   constexpr int NG = 32 / GS;
