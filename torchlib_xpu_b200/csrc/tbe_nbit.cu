@@ -2,7 +2,7 @@
 // {scale, bias} header per row, plus FP16 / FP32 tables, mixed per table.
 //
 // Two kernels share a call. INT8 and INT4 tables of at most 128 elements per row -- what inference
-// tables are -- go through the register gather of tbe_nbit_bags.cuh (one warp per bag, code words
+// tables are -- go through the register gather of tbe_nbit_bags.cuh (one warp per group of bags, code words
 // fetched straight into registers). Everything else (INT2, float rows, wider rows, rows that are
 // not 4-byte aligned) goes through the streaming gather engine of tbe_stream.cuh, described next;
 // each kernel skips the other's tables.
