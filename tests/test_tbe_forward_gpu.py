@@ -172,6 +172,30 @@ def test_forward_scatter_to_destinations():
         assert np.all(blk[:, :col0] == -7.0) and np.all(blk[:, col0 + 192:] == -7.0)
 
 
+def test_forward_groups_of_bags_across_destinations():
+    """Groups of bags with num_dests > 1: a destination's last row falls inside a group (rows_per_dest
+    is not a multiple of the group size), so a warp moves on to the next buffer between two bags."""
+    rng = workloads.rng_for(231)
+    Ds, rows, B = [128, 64, 128, 32], [500, 400, 300, 200], 30011
+    T = len(Ds)
+    W, wo, Do = helpers.float_tables(rng, rows, Ds, np.float16, -1, 1)
+    _, offsets, indices = helpers.ragged_bags(rng, T, B, rows, 0, 12, empty_fraction=0.2)
+    want = oracle.tbe_forward(W, oracle.FP16, wo, Do, B, indices, offsets)
+    G, rpd, total_D = 3, 10007, int(Do[-1])
+    col0, stride = 8, 8 + total_D + 8
+    bufs = [torch.full((rpd, stride), -7.0, dtype=torch.float16, device="cuda") for _ in range(G)]
+    cabi.forward(_dev(W), _dev(wo), _dev(Do), total_D, max(Ds), _dev(indices), _dev(offsets), B,
+                 outputs=bufs, output_stride=stride, output_col_offset=col0, rows_per_dest=rpd,
+                 output_dtype=torch.float16)
+    torch.cuda.synchronize()
+    for g, buf in enumerate(bufs):
+        blk = buf.float().cpu().numpy()
+        n = min(rpd, B - g * rpd)
+        np.testing.assert_allclose(blk[:n, col0:col0 + total_D], want[g * rpd:g * rpd + n], rtol=RTOL_FP16, atol=ATOL_FP16)
+        assert np.all(blk[:, :col0] == -7.0) and np.all(blk[:, col0 + total_D:] == -7.0)
+        assert np.all(blk[n:] == -7.0)
+
+
 def test_forward_named_fp32_config_against_oracle():
     """T=8, E=100k, D=128 fp32, B=2048, L~U{1..40}, uniform ids, seed 0 -- full size."""
     cfg = workloads.CONFIGS["tbe_fp32_fwd"]
