@@ -133,29 +133,40 @@ __global__ void __launch_bounds__(kBwdThreads)
     my_rows = sortable;
   }
   const uint32_t total = end > begin ? static_cast<uint32_t>(end - begin) : 0u;
-  for (uint32_t base = 0; base < total; base += 32) {
-    const uint32_t rel = base + lane;
-    int b = 0;
+  // four batches of 32 ids are requested before the first is turned into a key
+  constexpr int kBatches = 4;
+  for (uint32_t base = 0; base < total; base += 32 * kBatches) {
+    int64_t ids[kBatches];
 #pragma unroll
-    for (int step = 16; step > 0; step >>= 1) {
-      const int cand = b + step;
-      const uint32_t s = __shfl_sync(kFullMask, my_start, cand & 31);
-      if (cand < nb && s <= rel) b = cand;
+    for (int k = 0; k < kBatches; ++k) {
+      const uint32_t rel = base + 32 * k + lane;
+      ids[k] = rel < total ? load_index<IndexT>(p.indices, begin + rel) : 0;
     }
-    const int64_t rows = __shfl_sync(kFullMask, my_rows, b);
-    if (rel < total) {
-      const int64_t j = begin + rel;
-      int64_t idx = load_index<IndexT>(p.indices, j);
-      const uint32_t bag = static_cast<uint32_t>(bag0 + b);
-      uint32_t payload = kWeighted ? static_cast<uint32_t>(j) : bag;
-      if (idx < 0 || idx >= rows) {
-        if (p.status != nullptr) atomicOr(p.status, B200TBE_DEV_INDEX_OUT_OF_RANGE);
-        idx = 0;
-        payload = kInvalidPayload;
+#pragma unroll
+    for (int k = 0; k < kBatches; ++k) {
+      const uint32_t rel = base + 32 * k + lane;
+      int b = 0;
+#pragma unroll
+      for (int step = 16; step > 0; step >>= 1) {
+        const int cand = b + step;
+        const uint32_t s = __shfl_sync(kFullMask, my_start, cand & 31);
+        if (cand < nb && s <= rel) b = cand;
       }
-      keys[j] = static_cast<uint32_t>(idx);
-      vals[j] = payload;
-      if (kWeighted) p.bag_of_pos[j] = bag;
+      const int64_t rows = __shfl_sync(kFullMask, my_rows, b);
+      if (rel < total) {
+        const int64_t j = begin + rel;
+        int64_t idx = ids[k];
+        const uint32_t bag = static_cast<uint32_t>(bag0 + b);
+        uint32_t payload = kWeighted ? static_cast<uint32_t>(j) : bag;
+        if (idx < 0 || idx >= rows) {
+          if (p.status != nullptr) atomicOr(p.status, B200TBE_DEV_INDEX_OUT_OF_RANGE);
+          idx = 0;
+          payload = kInvalidPayload;
+        }
+        keys[j] = static_cast<uint32_t>(idx);
+        vals[j] = payload;
+        if (kWeighted) p.bag_of_pos[j] = bag;
+      }
     }
   }
 }
