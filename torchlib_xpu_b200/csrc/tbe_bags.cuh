@@ -22,6 +22,8 @@ namespace b200tbe {
 constexpr int kBagCtasPerSm = 32;
 constexpr int kBagLoads = 8;
 constexpr uint32_t kNoRow = 0xffffffffu;
+// lookups a warp walks in one call at most (positions are 32-bit ints that advance by up to 64)
+constexpr int kMaxStream = 0x7fffff00;
 
 // Bags per warp. A warp that walks a group of bags as one stream keeps its load rounds full and reads
 // ids ahead, which is worth up to 30 % (64-table fp16 step: 3.36 ms one bag per warp, 2.79 / 2.56 /
@@ -122,7 +124,7 @@ __device__ __forceinline__ void pool_float_bag(const BagLaunch<OT>& p, const cha
   constexpr int kLoads = kBagLoads;
   const int64_t start = load_index<IndexT>(p.offsets, bag);
   const int64_t end = load_index<IndexT>(p.offsets, bag + 1);
-  const int len = end - start > 0x7fffffff ? 0x7fffffff : static_cast<int>(end - start);
+  const int len = end - start > kMaxStream ? kMaxStream : static_cast<int>(end - start);
   const IndexT* idx = reinterpret_cast<const IndexT*>(p.indices) + start;
   const float* psw = kWeighted ? p.per_sample_weights + start : nullptr;
   const int vecs = row_bytes >> 4;
@@ -238,7 +240,7 @@ __device__ __forceinline__ void pool_float_bags(const BagLaunch<OT>& p, const ch
   int my_end = 0;
   if (lane < nb) {
     const int64_t e = load_index<IndexT>(p.offsets, bag0 + lane + 1) - begin;
-    my_end = e < 0 ? 0 : (e > 0x7fffffff ? 0x7fffffff : static_cast<int>(e));
+    my_end = e < 0 ? 0 : (e > kMaxStream ? kMaxStream : static_cast<int>(e));
   }
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {

@@ -150,7 +150,7 @@ __device__ __forceinline__ void pool_quantised_bags(const NbitParams& p, const c
   int my_end = 0;
   if (lane < nb) {
     const int64_t e = load_index<IndexT>(p.offsets, bag0 + lane + 1) - begin;
-    my_end = e < 0 ? 0 : (e > 0x7fffffff ? 0x7fffffff : static_cast<int>(e));
+    my_end = e < 0 ? 0 : (e > kMaxStream ? kMaxStream : static_cast<int>(e));
   }
 #pragma unroll
   for (int o = 1; o < 32; o <<= 1) {
