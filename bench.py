@@ -51,9 +51,13 @@ def measured_peak_gbs():
 
 
 class ClockSampler:
-    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    """nvidia-smi clock / throttle-reason samples taken while the GPU runs the step: the sampler is
+    started well before the warm-up steps (nvidia-smi needs a few hundred milliseconds to answer for
+    the first time), and the samples whose timestamps fall between the first warm-up step and the end
+    of the timed region are the ones reported; `samples_in_timed_region` says how many of those fell
+    into the timed steps themselves (the region is about a tenth of a second)."""
 
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -61,23 +65,93 @@ class ClockSampler:
         self.device_index = device_index
         self.proc = None
         self.path = None
+        self.t_load = self.t_timed = None
+        self.nvml_thread = None
 
     def start(self):
+        # NVML from a thread answers in well under a millisecond, nvidia-smi in a loop every ~100 ms:
+        # the thread is the sampler, the nvidia-smi loop the fallback
+        if self._start_nvml():
+            return
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.device_index), "--query-gpu=" + self.QUERY,
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                 "--format=csv,noheader,nounits", "-lms", "25"],
                 stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
 
+    def _start_nvml(self):
+        try:
+            import threading
+            import pynvml
+            pynvml.nvmlInit()
+            try:
+                uuid = "GPU-" + str(torch.cuda.get_device_properties(self.device_index).uuid)
+                handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                handle = pynvml.nvmlDeviceGetHandleByIndex(self.device_index)
+            reasons_of = getattr(pynvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+                pynvml.nvmlDeviceGetCurrentClocksThrottleReasons
+            self.nvml_max = float(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+            self.nvml_rows = []          # (time, sm MHz, reasons bit mask)
+            self.nvml_stop = threading.Event()
+
+            def loop():
+                while not self.nvml_stop.is_set():
+                    try:
+                        self.nvml_rows.append((time.time(),
+                                               float(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)),
+                                               int(reasons_of(handle))))
+                    except Exception:
+                        pass
+                    time.sleep(0.004)
+
+            self.nvml_thread = threading.Thread(target=loop, daemon=True)
+            self.nvml_thread.start()
+            return True
+        except Exception:
+            self.nvml_thread = None
+            return False
+
+    def mark_load(self):
+        """The GPU is busy with the step from now on (first warm-up step)."""
+        self.t_load = time.time()
+
+    def mark_timed(self):
+        self.t_timed = time.time()
+
+    @staticmethod
+    def _when(stamp):
+        import datetime
+        return datetime.datetime.strptime(stamp, "%Y/%m/%d %H:%M:%S.%f").timestamp()
+
     def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        t_end = time.time()
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0, "samples_in_timed_region": 0}
+        if self.nvml_thread is not None:
+            self.nvml_stop.set()
+            self.nvml_thread.join(timeout=2)
+            # NVML's bits: sw power cap 0x4, hw slowdown 0x8, sw thermal 0x20, hw thermal 0x40
+            names = ((0x8, "hw_slowdown"), (0x40, "hw_thermal_slowdown"), (0x20, "sw_thermal_slowdown"),
+                     (0x4, "sw_power_cap"))
+            rows = [r for r in self.nvml_rows if self.t_load is None or self.t_load <= r[0] <= t_end]
+            if rows:
+                out["sm_mhz"] = float(np.median([r[1] for r in rows]))
+                out["sm_max_mhz"] = self.nvml_max
+                out["samples"] = len(rows)
+                out["samples_in_timed_region"] = sum(1 for r in rows if self.t_timed is not None and r[0] >= self.t_timed)
+                mask = 0
+                for r in rows:
+                    mask |= r[2]
+                out["reasons"] = sorted(n for b, n in names if mask & b)
+            out["source"] = "NVML, sampled from a thread every 4 ms"
+            return out
         if self.proc is None:
             return out
-        time.sleep(0.15)
+        time.sleep(0.05)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -89,8 +163,16 @@ class ClockSampler:
                 f = [x.strip() for x in line.split(",")]
                 if len(f) < 9:
                     continue
+                try:
+                    when = self._when(f[0])
+                except Exception:
+                    continue
+                if self.t_load is not None and not (self.t_load <= when <= t_end + 0.02):
+                    continue
                 sm.append(float(f[1]))
                 out["sm_max_mhz"] = float(f[2])
+                if self.t_timed is not None and when >= self.t_timed:
+                    out["samples_in_timed_region"] += 1
                 for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
                                       "sw_power_cap"), f[5:9]):
                     if val.lower().startswith("active"):
@@ -733,18 +815,20 @@ def main():
         torch.cuda.synchronize()
 
     # ---- parity of this very workload, before anything is timed -----------------------------
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     checks = parity_checks(step, dist)
     barrier()
 
+    sampler.mark_load()
     for _ in range(args.warmup):
         step.step()
     barrier()
 
     # ---- device-resident timing: exactly K steps between barriers -------------------------
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     fwd_ms, bwd_ms = [], []
     barrier()
+    sampler.mark_timed()
     t_start = torch.cuda.Event(enable_timing=True)
     t_end = torch.cuda.Event(enable_timing=True)
     t_start.record()
