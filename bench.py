@@ -33,8 +33,8 @@ L2_FLUSH_BYTES = 512 << 20
 # rows x D=128, B=65536, about 1.67 M lookups -- from the ncu capture summarised in
 # profiles/tbe_step_one_table_traffic.md. Tables are processed one after another, each with its own
 # rows, ids and gradient columns, so a step of T tables moves T times this.
-FWD_TRAFFIC_PER_TABLE = 106.2e6   # lookup kernel: 101.5 MB read + 4.7 MB written
-BWD_TRAFFIC_PER_TABLE = 258.9e6   # 20 kernels of one b200tbe_backward call: 213.4 MB read + 45.5 MB written
+FWD_TRAFFIC_PER_TABLE = 107.2e6   # lookup kernel: 101.9 MB read + 5.3 MB written
+BWD_TRAFFIC_PER_TABLE = 254.9e6   # 20 kernels of one b200tbe_backward call: 213.4 MB read + 41.5 MB written
 TRAFFIC_NOTE = ("one-table ncu capture x tables (profiles/tbe_step_one_table_traffic.md); bytes a kernel leaves "
                 "dirty in L2 when it ends are not in its DRAM write counter")
 TABLES_OVERRIDE = None   # --tables: fewer tables for --only runs (small profiler captures)
