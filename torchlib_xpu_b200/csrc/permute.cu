@@ -5,8 +5,9 @@
 // Segments range from empty bags to whole tables, so the work is split by output ELEMENT, not by
 // segment: a CTA owns a tile of consecutive output elements, finds the segment of its first element
 // by a CTA-wide 256-ary search over the output offsets, walks the segment boundaries of the tile into shared
-// memory once, and then every thread copies elements whose source position is the input start of
-// their segment plus their distance from its output start. Reads and writes are coalesced inside
+// memory once, marks which of them holds each element of the tile (first elements marked, a running
+// maximum spreads the marks), and then every thread copies elements whose source position is the input
+// start of their segment plus their distance from its output start. Reads and writes are coalesced inside
 // a segment; per element the traffic is its bytes in and out plus one shared-memory lookup.
 #include "common.cuh"
 
@@ -107,30 +108,73 @@ __global__ void __launch_bounds__(kPermThreads)
   if (threadIdx.x == 0) seg_count = filled < kPermMaxSegs ? filled : kPermMaxSegs;
   __syncthreads();
   const int count = seg_count;
-#pragma unroll
-  for (int k = 0; k < kPermItems; ++k) {
-    const int64_t i = tile0 + static_cast<int64_t>(k) * kPermThreads + threadIdx.x;
-    if (i >= tile1) break;
-    int64_t src;
-    if (!overflow) {
-      int lo = 0, hi = count - 1;       // last listed segment whose output start is <= i
-      while (lo < hi) {
-        const int mid = (lo + hi + 1) >> 1;
-        if (seg_out_start[mid] <= i) {
-          lo = mid;
-        } else {
-          hi = mid - 1;
-        }
-      }
-      src = seg_in_start[lo] + (i - seg_out_start[lo]);
-    } else {
-      // more segment boundaries in one tile than the table holds (thousands of one-element
-      // segments): every element searches the global offsets itself
-      // (the last segment that starts at or before i is the non-empty one that holds it)
-      const int64_t seg = segment_of<OffT>(out_offsets, num_segments, i);
-      src = load_off<OffT>(in_offsets, static_cast<int64_t>(perm[seg])) + (i - load_off<OffT>(out_offsets, seg));
+  // Which listed segment holds each element of the tile: every segment marks its first element with
+  // its slot (slots grow with the position), and a running maximum over the tile spreads the marks.
+  // Thread t scans elements [16 t, 16 t + 16); the carry across threads is a warp / CTA max-scan.
+  __shared__ __align__(16) uint16_t slot_of[kPermTile];
+  __shared__ int warp_carry[kPermThreads / 32];
+  if (!overflow) {
+    uint4* z = reinterpret_cast<uint4*>(slot_of);
+    for (int q = threadIdx.x; q < kPermTile / 8; q += kPermThreads) z[q] = make_uint4(0u, 0u, 0u, 0u);
+    __syncthreads();
+    for (int k = threadIdx.x; k < count; k += kPermThreads) {
+      const int64_t at = seg_out_start[k] - tile0;
+      slot_of[at > 0 ? at : 0] = static_cast<uint16_t>(k);
     }
-    out[i] = in[src];
+    __syncthreads();
+    uint16_t* mine = slot_of + threadIdx.x * kPermItems;
+    int run = 0;
+#pragma unroll
+    for (int j = 0; j < kPermItems; ++j) run = max(run, static_cast<int>(mine[j]));
+    int incl = run;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(kFullMask, incl, o);
+      if ((threadIdx.x & 31) >= o) incl = max(incl, up);
+    }
+    if ((threadIdx.x & 31) == 31) warp_carry[threadIdx.x >> 5] = incl;
+    __syncthreads();
+    int carry = __shfl_up_sync(kFullMask, incl, 1);
+    if ((threadIdx.x & 31) == 0) carry = 0;
+    for (int w = 0; w < static_cast<int>(threadIdx.x >> 5); ++w) carry = max(carry, warp_carry[w]);
+#pragma unroll
+    for (int j = 0; j < kPermItems; ++j) {
+      carry = max(carry, static_cast<int>(mine[j]));
+      mine[j] = static_cast<uint16_t>(carry);
+    }
+    __syncthreads();
+  }
+  // eight elements at a time: their source positions first, then all eight loads, then the stores
+  constexpr int kBatch = 8;
+#pragma unroll
+  for (int k0 = 0; k0 < kPermItems; k0 += kBatch) {
+    int64_t src[kBatch];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int e = (k0 + u) * kPermThreads + threadIdx.x;
+      const int64_t i = tile0 + e;
+      src[u] = -1;
+      if (i >= tile1) continue;
+      if (!overflow) {
+        const int slot = slot_of[e];
+        src[u] = seg_in_start[slot] + (i - seg_out_start[slot]);
+      } else {
+        // more segment boundaries in one tile than the table holds (thousands of one-element
+        // segments): every element searches the global offsets itself
+        // (the last segment that starts at or before i is the non-empty one that holds it)
+        const int64_t seg = segment_of<OffT>(out_offsets, num_segments, i);
+        src[u] = load_off<OffT>(in_offsets, static_cast<int64_t>(perm[seg])) + (i - load_off<OffT>(out_offsets, seg));
+      }
+    }
+    ElemT v[kBatch];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u)
+      if (src[u] >= 0) v[u] = in[src[u]];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) {
+      const int64_t i = tile0 + static_cast<int64_t>(k0 + u) * kPermThreads + threadIdx.x;
+      if (src[u] >= 0) out[i] = v[u];
+    }
   }
 }
 
