@@ -370,7 +370,7 @@ def reference_arm(args, cfg, rank, json_out):
 # The other named configurations, single GPU, one kernel (or kernel group) each
 # --------------------------------------------------------------------------------------------
 def bench_others(peak_gbs, iters=20, only=None):
-    """only: None (all), or one of 'jagged', 'fp32', 'train', 'uniform', 'nbit', 'nv12', 'permute'."""
+    """only: None (all), or one of 'jagged', 'fp32', 'train', 'uniform', 'nbit', 'quantize', 'nv12', 'permute'."""
     res = {}
     flush = torch.empty(L2_FLUSH_BYTES, dtype=torch.uint8, device="cuda")
     gen = torch.Generator(device="cuda").manual_seed(99)
@@ -415,6 +415,8 @@ def _others_tbe(res, entry, flush, gen, iters, only):
         _bench_uniform(entry, flush, gen, iters)
     if only in (None, "nbit"):
         _bench_nbit(entry, flush, gen, iters)
+    if only in (None, "quantize"):
+        _bench_quantize(entry, flush, gen, iters)
     if only in (None, "nv12"):
         _bench_nv12(entry, flush, gen, iters)
     if only in (None, "permute"):
@@ -500,6 +502,26 @@ def _bench_uniform(entry, flush, gen, iters):
     entry("tbe_fp16_backward_adagrad(uniform ids, 16 GB of rows)", workloads.backward_bytes(n, U, D * 2, T, B, D, 2),
           ms, n, {"unique_rows": U, "kernels_per_call": backward_launches((E - 1).bit_length())})
     del W, mom, idx, grad, scratch
+
+
+def _bench_quantize(entry, flush, gen, iters):
+    # the step before the quantised lookup: 2 M fp32 rows of D=128 (1 GB) to INT8 / INT4 rows in the table
+    # layout (fp16 scale and bias in front, rows padded to 16 bytes), and INT8 rows back to fp32
+    rows, D = 2_000_000, 128
+    src = torch.rand((rows, D), device="cuda", generator=gen) * 2 - 1
+    for name, ty in (("INT8", cabi.INT8), ("INT4", cabi.INT4)):
+        out = cabi.quantize_rows(src, ty, 16, True)
+        ms, _ = time_launches(lambda: cabi.quantize_rows(src, ty, 16, True, out=out), max(5, iters // 2), flush)
+        entry("quantize_rows(fp32 -> %s, 2 M rows x 128)" % name, src.numel() * 4 + out.numel(), ms, None,
+              {"rows_per_s": rows / ms * 1e3})
+        if ty == cabi.INT8:
+            back = torch.empty_like(src)
+            ms, _ = time_launches(lambda: cabi.dequantize_rows(out, D, ty, 16, True, out=back), max(5, iters // 2), flush)
+            entry("dequantize_rows(INT8 -> fp32, 2 M rows x 128)", out.numel() + back.numel() * 4, ms, None,
+                  {"rows_per_s": rows / ms * 1e3})
+            del back
+        del out
+    del src
 
 
 def _bench_permute(entry, flush, gen, iters):
@@ -760,7 +782,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-others", action="store_true", help="skip the single-kernel configurations")
     ap.add_argument("--small", action="store_true", help="tiny tables, for profiler captures and smoke runs")
-    ap.add_argument("--only", default=None, choices=["jagged", "fp32", "train", "uniform", "nbit", "nv12", "permute", "step"],
+    ap.add_argument("--only", default=None, choices=["jagged", "fp32", "train", "uniform", "nbit", "quantize", "nv12", "permute", "step"],
                     help="run one single-GPU configuration alone (few launches; for profiler captures); "
                          "'step' is the bench step itself cut to --tables tables (default 2)")
     ap.add_argument("--iters", type=int, default=20, help="timed launches per single-GPU configuration")

@@ -339,22 +339,27 @@ def permute_segments(values, in_offsets, out_offsets, perm):
     return out
 
 
-def quantize_rows(src, ty, row_alignment=16, header_first=True):
+def quantize_rows(src, ty, row_alignment=16, header_first=True, out=None):
     """fp32/fp16 [rows, D] -> uint8 [rows, stride] row-wise quantised (b200tbe_quantize_rows)."""
     rows, D = src.shape
     stride = int(lib().b200tbe_quantized_row_bytes(D, ty, row_alignment))
     if stride < 0:
         raise B200TbeError("unsupported quantised type %r" % (ty,))
-    dst = torch.empty((rows, stride), dtype=torch.uint8, device=src.device)
+    dst = torch.empty((rows, stride), dtype=torch.uint8, device=src.device) if out is None else out
+    if dst.shape != (rows, stride) or dst.dtype != torch.uint8 or not dst.is_contiguous():
+        raise B200TbeError("out must be a contiguous uint8 [rows, %d] tensor" % stride)
     check(lib().b200tbe_quantize_rows(_p(src), _TORCH_TO_CODE[src.dtype], rows, D, ty, row_alignment,
                                       int(header_first), _p(dst), _stream()), "b200tbe_quantize_rows")
     return dst
 
 
-def dequantize_rows(rows_u8, D, ty, row_alignment=16, header_first=True, dtype=torch.float32):
+def dequantize_rows(rows_u8, D, ty, row_alignment=16, header_first=True, dtype=torch.float32, out=None):
     """uint8 [rows, stride] -> fp32/fp16 [rows, D] (b200tbe_dequantize_rows)."""
     rows = rows_u8.shape[0]
-    out = torch.empty((rows, D), dtype=dtype, device=rows_u8.device)
+    if out is None:
+        out = torch.empty((rows, D), dtype=dtype, device=rows_u8.device)
+    elif out.shape != (rows, D) or out.dtype != dtype or not out.is_contiguous():
+        raise B200TbeError("out must be a contiguous [rows, D] tensor of the requested dtype")
     check(lib().b200tbe_dequantize_rows(_p(rows_u8), rows, D, ty, row_alignment, int(header_first),
                                         _p(out), _TORCH_TO_CODE[dtype], _stream()),
           "b200tbe_dequantize_rows")
