@@ -180,25 +180,59 @@ __global__ void __launch_bounds__(kQThreads) quantize_rows_vec_kernel(QuantParam
       }
     }
   }
+  // R rows' minima and maxima across the warp. Reducing them one by one takes 10 shuffles a row;
+  // instead the lanes split the rows between them as they go: after the exchange over 16 lanes each
+  // half-warp carries half of the rows, after the one over 8 lanes (four rows) each quarter one row,
+  // and the remaining exchanges finish that row. Row r ends up in the lanes whose index / 8 (four
+  // rows) or / 16 (two rows) is r.
+  float my_mn, my_mx;
+  int my_row;     // the row whose extremes this lane ends up with
+  if constexpr (R == 4) {
+    const bool hi16 = lane & 16, hi8 = lane & 8;
+    float a[2], b2[2];
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      mn[r] = fminf(mn[r], __shfl_xor_sync(kFullMask, mn[r], o));
-      mx[r] = fmaxf(mx[r], __shfl_xor_sync(kFullMask, mx[r], o));
+    for (int i = 0; i < 2; ++i) {
+      const float omn = __shfl_xor_sync(kFullMask, hi16 ? mn[i] : mn[i + 2], 16);
+      const float omx = __shfl_xor_sync(kFullMask, hi16 ? mx[i] : mx[i + 2], 16);
+      a[i] = fminf(hi16 ? mn[i + 2] : mn[i], omn);
+      b2[i] = fmaxf(hi16 ? mx[i + 2] : mx[i], omx);
     }
+    const float omn = __shfl_xor_sync(kFullMask, hi8 ? a[0] : a[1], 8);
+    const float omx = __shfl_xor_sync(kFullMask, hi8 ? b2[0] : b2[1], 8);
+    my_mn = fminf(hi8 ? a[1] : a[0], omn);
+    my_mx = fmaxf(hi8 ? b2[1] : b2[0], omx);
+#pragma unroll
+    for (int o = 4; o > 0; o >>= 1) {
+      my_mn = fminf(my_mn, __shfl_xor_sync(kFullMask, my_mn, o));
+      my_mx = fmaxf(my_mx, __shfl_xor_sync(kFullMask, my_mx, o));
+    }
+    my_row = lane >> 3;
+  } else if constexpr (R == 2) {
+    const bool hi16 = lane & 16;
+    const float omn = __shfl_xor_sync(kFullMask, hi16 ? mn[0] : mn[1], 16);
+    const float omx = __shfl_xor_sync(kFullMask, hi16 ? mx[0] : mx[1], 16);
+    my_mn = fminf(hi16 ? mn[1] : mn[0], omn);
+    my_mx = fmaxf(hi16 ? mx[1] : mx[0], omx);
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) {
+      my_mn = fminf(my_mn, __shfl_xor_sync(kFullMask, my_mn, o));
+      my_mx = fmaxf(my_mx, __shfl_xor_sync(kFullMask, my_mx, o));
+    }
+    my_row = lane >> 4;
+  } else {
+    my_mn = mn[0];
+    my_mx = mx[0];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      my_mn = fminf(my_mn, __shfl_xor_sync(kFullMask, my_mn, o));
+      my_mx = fmaxf(my_mx, __shfl_xor_sync(kFullMask, my_mx, o));
+    }
+    my_row = 0;
   }
+  constexpr int kLanesPerRow = 32 / R;   // lane r * kLanesPerRow is the first that holds row r's scalars
   // The per-row scalars (fp16 bias and scale, the reciprocal) cost as many instructions for one
-  // lane as for 32, so lane r works them out for row r and hands them round; it also writes row r's
-  // header.
-  float my_mn = mn[0], my_mx = mx[0];
-#pragma unroll
-  for (int r = 1; r < R; ++r) {
-    if ((lane & (R - 1)) == r) {
-      my_mn = mn[r];
-      my_mx = mx[r];
-    }
-  }
+  // lane as for 32: every lane works them out for the row it holds and hands them round; the first
+  // lane of a row's share also writes its header.
   const __half hb = __float2half_rn(my_mn);
   const float my_bias = __half2float(hb);
   const float range = my_mx - my_bias;
@@ -212,8 +246,8 @@ __global__ void __launch_bounds__(kQThreads) quantize_rows_vec_kernel(QuantParam
   const uint32_t my_header = static_cast<uint32_t>(__half_as_ushort(hs)) | (static_cast<uint32_t>(__half_as_ushort(hb)) << 16);
   // header and padding as whole words where the row's layout allows it
   const bool words = (payload & 3) == 0;
-  if (lane < R && row0 + lane < p.rows) {
-    uint8_t* out = p.dst + (row0 + lane) * p.dst_stride;
+  if ((lane & (kLanesPerRow - 1)) == 0 && row0 + my_row < p.rows) {
+    uint8_t* out = p.dst + (row0 + my_row) * p.dst_stride;
     uint8_t* header = p.header_first ? out : out + payload;
     if (words) {
       *reinterpret_cast<uint32_t*>(header) = my_header;
@@ -226,8 +260,8 @@ __global__ void __launch_bounds__(kQThreads) quantize_rows_vec_kernel(QuantParam
   }
 #pragma unroll
   for (int r = 0; r < R; ++r) {
-    const float bias = __shfl_sync(kFullMask, my_bias, r);
-    const float inv = __shfl_sync(kFullMask, my_inv, r);
+    const float bias = __shfl_sync(kFullMask, my_bias, r * kLanesPerRow);
+    const float inv = __shfl_sync(kFullMask, my_inv, r * kLanesPerRow);
     if (row0 + r >= p.rows) continue;
     uint8_t* out = p.dst + (row0 + r) * p.dst_stride;
     uint8_t* body = out + (p.header_first ? 4 : 0);
