@@ -273,9 +273,12 @@ __global__ void __launch_bounds__(kQThreads) quantize_rows_vec_kernel(QuantParam
       unsigned word = 0;
 #pragma unroll
       for (int k = 0; k < 4; ++k) {
-        int q = __float2int_rn((e[k] - bias) * inv);
-        q = q < 0 ? 0 : (q > qmax ? qmax : q);
-        word |= static_cast<unsigned>(q) << (k * p.bits);
+        // round to nearest even; the conversion saturates at 0 and 255 (and turns NaN into 0), as
+        // __float2int_rn followed by the clamp does
+        unsigned q;
+        asm("cvt.rni.u8.f32 %0, %1;" : "=r"(q) : "f"((e[k] - bias) * inv));
+        q = q > static_cast<unsigned>(qmax) ? static_cast<unsigned>(qmax) : q;
+        word |= q << (k * p.bits);
       }
       if (p.bits == 8) {
         *reinterpret_cast<uint32_t*>(body + 4 * j) = word;
