@@ -86,15 +86,12 @@ __device__ __forceinline__ uint32_t byte_of(uint4 v, int i) {
 // channel one multiply by 255 and one saturating conversion. The products with the matrix's zeros
 // are +-0 and adding them changes nothing.
 struct Nv12Tables {
-  float luma[256];
   float2 from_u[256];   // {U into G, U into B}
   float2 from_v[256];   // {V into R, V into G}
 };
 
 __device__ __forceinline__ void fill_tables(Nv12Tables& t, bool fullrange) {
   for (int i = threadIdx.x; i < 256; i += blockDim.x) {
-    const float b = static_cast<float>(i);
-    t.luma[i] = __fmul_rn(fullrange ? __fdiv_rn(b, 255.0f) : __fdiv_rn(__fsub_rn(b, 16.0f), 219.0f), 1.0f);
     const Chroma c = chroma_terms(i, i, fullrange);   // the U and the V term are the same function
     t.from_u[i] = make_float2(__fmul_rn(c.s1, -0.187324f), __fmul_rn(c.s1, 1.8556f));
     t.from_v[i] = make_float2(__fmul_rn(c.s2, 1.5748f), __fmul_rn(c.s2, -0.468124f));
@@ -108,15 +105,29 @@ __device__ __forceinline__ uint32_t to_byte_sat(float f) {
   return r;
 }
 
+// The normalised luma without a table and without a division: (y - sub) / div for a byte y equals, bit
+// for bit, one refinement step on the product with the rounded reciprocal -- q0 = a * r,
+// q = fma(fma(-q0, div, a), r, q0) -- for all 256 bytes and both ranges (checked exhaustively on the
+// host against IEEE division; the bit-exact tests against the reference's kernel cover it again).
+struct LumaScale {
+  float sub, div, recip;
+};
+__device__ __forceinline__ float luma_of(uint32_t y, const LumaScale& k) {
+  const float a = __fsub_rn(static_cast<float>(y), k.sub);
+  const float q0 = __fmul_rn(a, k.recip);
+  return __fmaf_rn(__fmaf_rn(-q0, k.div, a), k.recip, q0);
+}
+
 // 16 pixels of one row -> 48 bytes, three aligned 16-byte stores.
-__device__ __forceinline__ void convert_row16(const Nv12Tables& t, uint4 luma, uint4 chroma, uint8_t* dst) {
+__device__ __forceinline__ void convert_row16(const Nv12Tables& t, const LumaScale& ls, uint4 luma, uint4 chroma,
+                                              uint8_t* dst) {
   uint32_t bytes[48];
 #pragma unroll
   for (int pair = 0; pair < 8; ++pair) {
     const float2 fu = t.from_u[byte_of(chroma, 2 * pair)], fv = t.from_v[byte_of(chroma, 2 * pair + 1)];
 #pragma unroll
     for (int s = 0; s < 2; ++s) {
-      const float s0 = t.luma[byte_of(luma, 2 * pair + s)];
+      const float s0 = luma_of(byte_of(luma, 2 * pair + s), ls);
       bytes[3 * (2 * pair + s) + 0] = to_byte_sat(__fadd_rn(s0, fv.x));
       bytes[3 * (2 * pair + s) + 1] = to_byte_sat(__fadd_rn(__fadd_rn(s0, fu.x), fv.y));
       bytes[3 * (2 * pair + s) + 2] = to_byte_sat(__fadd_rn(s0, fu.y));
@@ -157,8 +168,10 @@ __global__ void __launch_bounds__(kNv12Threads)
   if (second) luma1 = ldg_stream16(y_plane + surface_offset(x, y0 + 1, stride, tiled));
   fill_tables(tables, fullrange);
   __syncthreads();
-  if (mine) convert_row16(tables, luma0, chroma, rgb + 3 * (static_cast<size_t>(y0) * width + x));
-  if (second) convert_row16(tables, luma1, chroma, rgb + 3 * (static_cast<size_t>(y0 + 1) * width + x));
+  const LumaScale ls = fullrange ? LumaScale{0.0f, 255.0f, __fdiv_rn(1.0f, 255.0f)}
+                                 : LumaScale{16.0f, 219.0f, __fdiv_rn(1.0f, 219.0f)};
+  if (mine) convert_row16(tables, ls, luma0, chroma, rgb + 3 * (static_cast<size_t>(y0) * width + x));
+  if (second) convert_row16(tables, ls, luma1, chroma, rgb + 3 * (static_cast<size_t>(y0 + 1) * width + x));
 }
 
 __global__ void __launch_bounds__(kNv12Threads)
