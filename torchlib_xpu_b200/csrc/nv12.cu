@@ -10,10 +10,12 @@
 // pointers / pitch are not 16-byte aligned, take a one-thread-per-pixel path.
 //
 // Arithmetic: every fp32 operation is issued with an explicit round-to-nearest intrinsic in the
-// order the CPU oracle uses, so the two agree bit for bit (no fused multiply-add). The divisions of
-// the normalisation would make the kernel issue-bound (about 67 instructions per pixel measured),
-// so the block path reads every one-byte term from 256-entry tables built with those same
-// operations (about 28 instructions per pixel).
+// order the CPU oracle uses, so the two agree bit for bit. The divisions of the normalisation would
+// make the kernel issue-bound (about 67 instructions per pixel measured). Their dividends are bytes,
+// though, and for a byte the quotient equals one refinement step on the product with the rounded
+// reciprocal (two fused multiply-adds, exact for all 256 values: luma_of, chroma_of), so the block
+// path divides nothing; tables of the one-byte terms in shared memory, the version before this one,
+// were bound by bank conflicts on random pixels (16.5 us per 4K frame against 12.6).
 #include "common.cuh"
 
 namespace b200tbe {
@@ -79,25 +81,6 @@ __device__ __forceinline__ uint32_t byte_of(uint4 v, int i) {
   return (w >> ((i & 3) * 8)) & 0xffu;
 }
 
-// A byte has 256 values, so every term of the conversion that depends on one byte alone is a table:
-// the normalised luma, and the four non-trivial chroma products (V into R, U and V into G, U into
-// B). The tables are filled per CTA with exactly the operations of pixel_rgb, so a pixel is two
-// shared-memory reads (one for its luma, two 8-byte ones per chroma pair), four adds, and per
-// channel one multiply by 255 and one saturating conversion. The products with the matrix's zeros
-// are +-0 and adding them changes nothing.
-struct Nv12Tables {
-  float2 from_u[256];   // {U into G, U into B}
-  float2 from_v[256];   // {V into R, V into G}
-};
-
-__device__ __forceinline__ void fill_tables(Nv12Tables& t, bool fullrange) {
-  for (int i = threadIdx.x; i < 256; i += blockDim.x) {
-    const Chroma c = chroma_terms(i, i, fullrange);   // the U and the V term are the same function
-    t.from_u[i] = make_float2(__fmul_rn(c.s1, -0.187324f), __fmul_rn(c.s1, 1.8556f));
-    t.from_v[i] = make_float2(__fmul_rn(c.s2, 1.5748f), __fmul_rn(c.s2, -0.468124f));
-  }
-}
-
 // x * 255 truncated to a byte; the conversion saturates at 0 and 255, which is the clamp.
 __device__ __forceinline__ uint32_t to_byte_sat(float f) {
   uint32_t r;
@@ -118,13 +101,26 @@ __device__ __forceinline__ float luma_of(uint32_t y, const LumaScale& k) {
   return __fmaf_rn(__fmaf_rn(-q0, k.div, a), k.recip, q0);
 }
 
+// The same for a chroma byte: (c - 128) / 224, or in the reference's "full range" branch
+// (c - 128) / 255 - 0.5.
+__device__ __forceinline__ float chroma_of(uint32_t c, const LumaScale& k) {
+  const float a = __fsub_rn(static_cast<float>(c), 128.0f);
+  const float q0 = __fmul_rn(a, k.recip);
+  const float q = __fmaf_rn(__fmaf_rn(-q0, k.div, a), k.recip, q0);
+  return __fsub_rn(q, k.sub);      // sub is 0 or 0.5: subtracting +0 changes nothing
+}
+
 // 16 pixels of one row -> 48 bytes, three aligned 16-byte stores.
-__device__ __forceinline__ void convert_row16(const Nv12Tables& t, const LumaScale& ls, uint4 luma, uint4 chroma,
+__device__ __forceinline__ void convert_row16(const LumaScale& ls, const LumaScale& cs, uint4 luma, uint4 chroma,
                                               uint8_t* dst) {
   uint32_t bytes[48];
 #pragma unroll
   for (int pair = 0; pair < 8; ++pair) {
-    const float2 fu = t.from_u[byte_of(chroma, 2 * pair)], fv = t.from_v[byte_of(chroma, 2 * pair + 1)];
+    // {U into G, U into B} and {V into R, V into G}; the products with the matrix's zeros are +-0 and
+    // adding them changes nothing
+    const float cu = chroma_of(byte_of(chroma, 2 * pair), cs), cv = chroma_of(byte_of(chroma, 2 * pair + 1), cs);
+    const float2 fu = make_float2(__fmul_rn(cu, -0.187324f), __fmul_rn(cu, 1.8556f));
+    const float2 fv = make_float2(__fmul_rn(cv, 1.5748f), __fmul_rn(cv, -0.468124f));
 #pragma unroll
     for (int s = 0; s < 2; ++s) {
       const float s0 = luma_of(byte_of(luma, 2 * pair + s), ls);
@@ -143,14 +139,11 @@ __device__ __forceinline__ void convert_row16(const Nv12Tables& t, const LumaSca
   out[2] = make_uint4(w[8], w[9], w[10], w[11]);
 }
 
-// A plain grid, one block of 16 pixels x 2 rows per thread, 40 registers (measured: a persistent
-// grid striding over one-row blocks with the tables built once per CTA is 17 % slower, forcing 32
-// registers for a single wave on a 4K frame 22 % slower).
+// A plain grid, one block of 16 pixels x 2 rows per thread, no shared memory.
 __global__ void __launch_bounds__(kNv12Threads)
     nv12_to_rgb_blocks_kernel(const uint8_t* __restrict__ y_plane, const uint8_t* __restrict__ uv_plane,
                               uint8_t* __restrict__ rgb, int width, int height, int stride,
                               bool fullrange, bool tiled) {
-  __shared__ Nv12Tables tables;
   const int groups = width >> 4;                 // 16-pixel blocks per row
   const int64_t block = static_cast<int64_t>(blockIdx.x) * kNv12Threads + threadIdx.x;
   const int64_t total = static_cast<int64_t>(groups) * ((height + 1) >> 1);
@@ -159,19 +152,18 @@ __global__ void __launch_bounds__(kNv12Threads)
   const int x = mine ? static_cast<int>(block - static_cast<int64_t>(gy) * groups) << 4 : 0;
   const int y0 = gy * 2;
   const bool second = mine && y0 + 1 < height;
-  // the loads are on their way while the tables are filled
   uint4 chroma = make_uint4(0u, 0u, 0u, 0u), luma0 = chroma, luma1 = chroma;
   if (mine) {
     chroma = ldg_stream16(uv_plane + surface_offset(x, gy, stride, tiled));
     luma0 = ldg_stream16(y_plane + surface_offset(x, y0, stride, tiled));
   }
   if (second) luma1 = ldg_stream16(y_plane + surface_offset(x, y0 + 1, stride, tiled));
-  fill_tables(tables, fullrange);
-  __syncthreads();
   const LumaScale ls = fullrange ? LumaScale{0.0f, 255.0f, __fdiv_rn(1.0f, 255.0f)}
                                  : LumaScale{16.0f, 219.0f, __fdiv_rn(1.0f, 219.0f)};
-  if (mine) convert_row16(tables, ls, luma0, chroma, rgb + 3 * (static_cast<size_t>(y0) * width + x));
-  if (second) convert_row16(tables, ls, luma1, chroma, rgb + 3 * (static_cast<size_t>(y0 + 1) * width + x));
+  const LumaScale cs = fullrange ? LumaScale{0.5f, 255.0f, __fdiv_rn(1.0f, 255.0f)}
+                                 : LumaScale{0.0f, 224.0f, __fdiv_rn(1.0f, 224.0f)};
+  if (mine) convert_row16(ls, cs, luma0, chroma, rgb + 3 * (static_cast<size_t>(y0) * width + x));
+  if (second) convert_row16(ls, cs, luma1, chroma, rgb + 3 * (static_cast<size_t>(y0 + 1) * width + x));
 }
 
 __global__ void __launch_bounds__(kNv12Threads)
