@@ -76,9 +76,11 @@ __device__ __forceinline__ void pixel_rgb(uint32_t y, Chroma c, bool fullrange, 
   }
 }
 
-__device__ __forceinline__ uint32_t byte_of(uint4 v, int i) {
+// Byte i of the vector as the float 2^23 + byte: the byte dropped into the mantissa of 8388608.0 by one
+// permute (exact; the caller subtracts 2^23 together with its own offset).
+__device__ __forceinline__ float byte_plus_2p23(uint4 v, int i) {
   const uint32_t w = i < 4 ? v.x : (i < 8 ? v.y : (i < 12 ? v.z : v.w));
-  return (w >> ((i & 3) * 8)) & 0xffu;
+  return __uint_as_float(__byte_perm(w, 0x4b000000u, 0x7540u + (i & 3)));
 }
 
 // x * 255 truncated to a byte; the conversion saturates at 0 and 255, which is the clamp.
@@ -95,16 +97,16 @@ __device__ __forceinline__ uint32_t to_byte_sat(float f) {
 struct LumaScale {
   float sub, div, recip;
 };
-__device__ __forceinline__ float luma_of(uint32_t y, const LumaScale& k) {
-  const float a = __fsub_rn(static_cast<float>(y), k.sub);
+__device__ __forceinline__ float luma_of(float y_plus_2p23, const LumaScale& k) {
+  const float a = __fsub_rn(y_plus_2p23, 8388608.0f + k.sub);      // both exact
   const float q0 = __fmul_rn(a, k.recip);
   return __fmaf_rn(__fmaf_rn(-q0, k.div, a), k.recip, q0);
 }
 
 // The same for a chroma byte: (c - 128) / 224, or in the reference's "full range" branch
 // (c - 128) / 255 - 0.5.
-__device__ __forceinline__ float chroma_of(uint32_t c, const LumaScale& k) {
-  const float a = __fsub_rn(static_cast<float>(c), 128.0f);
+__device__ __forceinline__ float chroma_of(float c_plus_2p23, const LumaScale& k) {
+  const float a = __fsub_rn(c_plus_2p23, 8388608.0f + 128.0f);
   const float q0 = __fmul_rn(a, k.recip);
   const float q = __fmaf_rn(__fmaf_rn(-q0, k.div, a), k.recip, q0);
   return __fsub_rn(q, k.sub);      // sub is 0 or 0.5: subtracting +0 changes nothing
@@ -118,12 +120,12 @@ __device__ __forceinline__ void convert_row16(const LumaScale& ls, const LumaSca
   for (int pair = 0; pair < 8; ++pair) {
     // {U into G, U into B} and {V into R, V into G}; the products with the matrix's zeros are +-0 and
     // adding them changes nothing
-    const float cu = chroma_of(byte_of(chroma, 2 * pair), cs), cv = chroma_of(byte_of(chroma, 2 * pair + 1), cs);
+    const float cu = chroma_of(byte_plus_2p23(chroma, 2 * pair), cs), cv = chroma_of(byte_plus_2p23(chroma, 2 * pair + 1), cs);
     const float2 fu = make_float2(__fmul_rn(cu, -0.187324f), __fmul_rn(cu, 1.8556f));
     const float2 fv = make_float2(__fmul_rn(cv, 1.5748f), __fmul_rn(cv, -0.468124f));
 #pragma unroll
     for (int s = 0; s < 2; ++s) {
-      const float s0 = luma_of(byte_of(luma, 2 * pair + s), ls);
+      const float s0 = luma_of(byte_plus_2p23(luma, 2 * pair + s), ls);
       bytes[3 * (2 * pair + s) + 0] = to_byte_sat(__fadd_rn(s0, fv.x));
       bytes[3 * (2 * pair + s) + 1] = to_byte_sat(__fadd_rn(__fadd_rn(s0, fu.x), fv.y));
       bytes[3 * (2 * pair + s) + 2] = to_byte_sat(__fadd_rn(s0, fu.y));
