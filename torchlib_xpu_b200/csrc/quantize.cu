@@ -319,15 +319,22 @@ __global__ void __launch_bounds__(kQThreads) dequantize_rows_vec_kernel(DequantP
   const int payload = p.D * p.bits / 8;
   const unsigned mask = (1u << p.bits) - 1u;
   unsigned word[R][V];
-  unsigned hdr[R][4];
+  unsigned hdr[R];                 // {scale, bias} as stored: two fp16
+  const bool header_word = p.header_first || (payload & 3) == 0;   // the header is 4-byte aligned
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     const uint8_t* in = p.src + (row0 + r) * p.src_stride;
     const uint8_t* body = in + (p.header_first ? 4 : 0);
     const uint8_t* header = p.header_first ? in : in + payload;
     const bool live = row0 + r < p.rows;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) hdr[r][k] = live ? header[k] : 0u;
+    hdr[r] = 0u;
+    if (live) {
+      if (header_word) {
+        hdr[r] = __ldg(reinterpret_cast<const uint32_t*>(header));
+      } else {
+        hdr[r] = header[0] | (header[1] << 8) | (header[2] << 16) | (static_cast<unsigned>(header[3]) << 24);
+      }
+    }
 #pragma unroll
     for (int v = 0; v < V; ++v) {
       const int j = v * 32 + lane;
@@ -346,8 +353,8 @@ __global__ void __launch_bounds__(kQThreads) dequantize_rows_vec_kernel(DequantP
 #pragma unroll
   for (int r = 0; r < R; ++r) {
     if (row0 + r >= p.rows) break;
-    const float scale = __half2float(__ushort_as_half(static_cast<unsigned short>(hdr[r][0] | (hdr[r][1] << 8))));
-    const float bias = __half2float(__ushort_as_half(static_cast<unsigned short>(hdr[r][2] | (hdr[r][3] << 8))));
+    const float scale = __half2float(__ushort_as_half(static_cast<unsigned short>(hdr[r] & 0xffffu)));
+    const float bias = __half2float(__ushort_as_half(static_cast<unsigned short>(hdr[r] >> 16)));
     T* y = static_cast<T*>(p.dst) + (row0 + r) * p.D;
 #pragma unroll
     for (int v = 0; v < V; ++v) {
