@@ -501,7 +501,24 @@ def _bench_uniform(entry, flush, gen, iters):
     ms, _ = time_launches(bwd, max(5, iters // 2), flush)
     entry("tbe_fp16_backward_adagrad(uniform ids, 16 GB of rows)", workloads.backward_bytes(n, U, D * 2, T, B, D, 2),
           ms, n, {"unique_rows": U, "kernels_per_call": backward_launches((E - 1).bit_length())})
-    del W, mom, idx, grad, scratch
+    del W, mom, idx, grad, scratch, out
+    # the same lookup on rows of 128 and 64 bytes (D = 64, 32): random rows this short are no longer bound
+    # by bytes but by how many rows a second HBM serves, which is what the quantised tables' rows meet
+    for D in (64, 32):
+        E = 16_000_000 * 128 // D
+        idx = torch.randint(0, E, (T * B * L,), device="cuda", generator=gen)
+        U = sum(int(torch.unique(idx[t * B * L:(t + 1) * B * L]).numel()) for t in range(T))
+        W = uniform_half_table(T * E * D, -0.01, 0.01, gen)
+        wo = torch.arange(T, device="cuda", dtype=torch.int64) * (E * D)
+        Do = torch.arange(T + 1, device="cuda", dtype=torch.int32) * D
+        out = torch.empty((B, T * D), device="cuda", dtype=torch.float16)
+        fwd = lambda: cabi.forward(W, wo, Do, T * D, D, idx, offs, B, outputs=[out], output_stride=T * D,
+                                   rows_per_dest=B, output_dtype=torch.float16)
+        fwd()
+        ms, _ = time_launches(fwd, max(5, iters // 2), flush)
+        entry("tbe_fp16_forward(uniform ids, 16 GB of %d-byte rows)" % (D * 2),
+              workloads.forward_bytes(n, U, D * 2, T, B, D, 2), ms, n, {"unique_rows": U})
+        del W, idx, out
 
 
 def _bench_quantize(entry, flush, gen, iters):
